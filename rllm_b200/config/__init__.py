@@ -1,4 +1,5 @@
 from .base import (ConfigError, LayerSpec, ModelConfig, ModelSpec, PartSpec, RunEntry)
+from .divuzen import DivuzenConfig
 from .falalix import FalalixConfig
 from .govopel import GovopelConfig
 from .qwen3 import Qwen3Config
@@ -8,7 +9,8 @@ from .registry import (config_class, config_from_dict, load_config, register_arc
 register_architecture("Qwen3ForCausalLM", Qwen3Config)
 register_architecture("Falalix", FalalixConfig)
 register_architecture("Govopel", GovopelConfig)
+register_architecture("Divuzen", DivuzenConfig)
 
-__all__ = ["ConfigError", "LayerSpec", "ModelConfig", "ModelSpec", "PartSpec", "RunEntry", "Qwen3Config", "FalalixConfig", "GovopelConfig",
+__all__ = ["ConfigError", "LayerSpec", "ModelConfig", "ModelSpec", "PartSpec", "RunEntry", "Qwen3Config", "FalalixConfig", "GovopelConfig", "DivuzenConfig",
            "config_class", "config_from_dict", "load_config", "register_architecture",
            "supported_architectures"]

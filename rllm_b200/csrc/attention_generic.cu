@@ -14,7 +14,8 @@
 // are the leading entries of the key rows themselves, v_cache == k_cache).
 // chunk > 0: positions are cut into runs of `chunk` counted from 0 and a token sees only the keys of
 // its own run (p >= pos - pos % chunk).  softcap > 0: a score s becomes softcap * tanh(s / softcap)
-// before the softmax.
+// before the softmax.  sink (one number per query head, or null): the softmax's denominator also holds
+// exp(sink[h]), which stands for no key and adds no value.
 //
 // Formula: crates/rllm-cpu/src/lib.rs:389-425 of AxiomOperator/rllm; its device
 // counterpart is paged_attention (crates/rllm-cuda/kernels/kernels.cu:1634-1690).
@@ -33,7 +34,7 @@ paged_attention_generic_kernel(const TQ* q, const TC* k_cache,
                                const int* __restrict__ positions, const int* __restrict__ seq_ids,
                                const int* __restrict__ block_table, int table_stride, int H, int K,
                                int hd, int hdv, int bs, float scale, int window, int keep_first, int n_pages,
-                               int* err, int chunk, float softcap, int v_ld) {
+                               int* err, int chunk, float softcap, int v_ld, const float* __restrict__ sink) {
     extern __shared__ float smem[];
     pdl_wait();
     pdl_launch_dependents();
@@ -57,7 +58,8 @@ paged_attention_generic_kernel(const TQ* q, const TC* k_cache,
     float acc[ATT_MAX_ACC];
 #pragma unroll
     for (int a = 0; a < ATT_MAX_ACC; ++a) acc[a] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
+    // a sink: a term exp(sink[h]) in the denominator that has no key and no value
+    float m_run = sink ? sink[h] : -INFINITY, l_run = sink ? 1.f : 0.f;
 
     // two runs of keys: the kept first ones outside the window, then the window
     const int kept = keep_first < first ? keep_first : first;
@@ -116,7 +118,7 @@ RLLM_API int rllm_paged_attention_generic(const void* q, int q_dtype, const void
                                           const int* block_table, int table_stride, int n, int H,
                                           int K, int hd, int hdv, int bs, float scale, int window, int keep_first,
                                           int n_pages, int* err, int chunk, float softcap, int v_ld,
-                                          cudaStream_t stream) {
+                                          const float* sink, cudaStream_t stream) {
     if (n <= 0) return 0;
     if (v_ld <= 0) v_ld = hdv;
     if (chunk < 0 || v_ld < hdv) return (int)cudaErrorInvalidValue;
@@ -130,11 +132,11 @@ RLLM_API int rllm_paged_attention_generic(const void* q, int q_dtype, const void
         return rllm_launch(paged_attention_generic_kernel<float, float, float>, grid, dim3(ATT_THREADS), smem,
                            stream, (const float*)q, (const float*)k_cache, (const float*)v_cache, (float*)out,
                            positions, seq_ids, block_table, table_stride, H, K, hd, hdv, bs, scale, window, keep_first, n_pages,
-                           err, chunk, softcap, v_ld);
+                           err, chunk, softcap, v_ld, sink);
     return rllm_launch(paged_attention_generic_kernel<bf16, bf16, bf16>, grid, dim3(ATT_THREADS), smem, stream,
                        (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, positions,
                        seq_ids, block_table, table_stride, H, K, hd, hdv, bs, scale, window, keep_first, n_pages, err,
-                       chunk, softcap, v_ld);
+                       chunk, softcap, v_ld, sink);
 }
 
 // the packed-argument forms (common.cuh) for the host runtime's replay of recorded launches

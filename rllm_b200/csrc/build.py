@@ -33,6 +33,7 @@ NVCC_FLAGS = [
 LIBRARIES = {
     "core": (["elementwise.cu", "rowwise.cu", "headwise.cu", "attention_generic.cu", "gemm_plain.cu", "sampling.cu"], []),
     "recur": (["recurrent.cu"], []),
+    "moe": (["moe.cu"], []),
     "blas": (["gemm_lib.cu"], ["-lcublas"]),
     "fast": (["skinny_gemm.cu"], []),
     "attn": (["attention_flash.cu"], []),

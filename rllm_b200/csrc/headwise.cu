@@ -13,6 +13,11 @@
 //   latent_rope_store  one cache row per token [normed latent (rank) | rotated shared key part (r)],
 //                      and the rotated part of every query head copied behind that head's latent-space
 //                      query.
+//   head_norm_rope_store  per head of a [q | k | v] projection row: RMS norm with a weight, then the
+//                      rotation of the first `rot` entries (either pair layout); queries out, keys and
+//                      values (heads of another size) into the paged cache; rows of queries only too.
+//   join_norm_rows     x += y / rms(y) * w_out and out = x / rms(x) * w_next in one pass: a norm on a
+//                      sublayer's output followed by the norm in front of the next sublayer.
 //   glu_clamped        out = g * sigmoid(alpha * g) * (u + shift), g = min(gate, limit),
 //                      u = clamp(up, -limit, limit).
 //   softcap_rows       x = cap * tanh(x / cap) in place.
@@ -386,6 +391,146 @@ RLLM_API int rllm_masked_softmax_rows(const float* S, long long ld, void* P, lon
                        pos0, n_cols, scale, softcap, chunk);
 }
 
+// ------------------------------------------------------------------ norm per head, then rotate, then store
+// Grid (token, group of 4 heads), one warp per head; heads 0..H-1 are queries, H..H+G-1 keys (only
+// with has_kv).  row = [q (H*hd) | k (G*hd) | v (G*hdv)], rows ld apart.  A query or key head is divided
+// by its root mean square and multiplied by a weight of hd entries shared by all heads (null: no norm),
+// then its first `rot` entries are rotated by the token's angles: pairs (2i, 2i + 1) when `pairs`, else
+// (i, i + rot/2).  Queries go to q_out, keys and values (heads of hdv entries, as projected) into the
+// pages.
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(128)
+head_norm_rope_store_kernel(const TI* row_base, long long ld, const float* __restrict__ q_w,
+                            const float* __restrict__ k_w, const float2* cs_table, int rot, int pairs,
+                            const int* __restrict__ slots, TO* q_out, TO* k_cache, TO* v_cache, int H, int G, int hd,
+                            int hdv, int bs, float eps, int has_kv, int write_kv, int n_slots, int* err) {
+    extern __shared__ float sm[];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int head = blockIdx.y * 4 + warp;
+    if (head >= H + (has_kv ? G : 0)) return;
+    float* v = sm + (size_t)warp * hd;
+    const TI* src = row_base + (size_t)t * ld + (size_t)head * hd;
+    float ss = 0.f;
+    for (int i = lane; i < hd; i += 32) {
+        const float x = to_f<TI>(src[i]);
+        v[i] = x;
+        ss += x * x;
+    }
+    ss = warp_sum(ss);
+    const bool is_key = head >= H;
+    const float* w = is_key ? k_w : q_w;
+    if (w) {
+        const float rs = 1.0f / sqrtf(ss / (float)hd + eps);
+        for (int i = lane; i < hd; i += 32) v[i] = v[i] * rs * w[i];
+    }
+    __syncwarp();
+    int slot = -1;
+    if (is_key && write_kv) {
+        slot = slots[t];
+        if (slot >= n_slots) {
+            if (lane == 0 && err) atomicExch(err, RLLM_ERR_SLOT);
+            slot = -1;
+        }
+    }
+    const int half = rot >> 1;
+    const float2* cs = cs_table + (size_t)t * half;
+    for (int i = lane; i < half; i += 32) {
+        const float2 a = cs[i];
+        const int iu = pairs ? 2 * i : i, iv = pairs ? 2 * i + 1 : i + half;
+        const float u = v[iu], x = v[iv];
+        v[iu] = u * a.x - x * a.y;
+        v[iv] = x * a.x + u * a.y;
+    }
+    __syncwarp();
+    if (!is_key) {
+        TO* dst = q_out + ((size_t)t * H + head) * hd;
+        for (int i = lane; i < hd; i += 32) dst[i] = from_f<TO>(v[i]);
+    } else if (slot >= 0) {
+        const int kh = head - H;
+        const size_t page_row = ((size_t)(slot / bs) * G + kh) * bs + slot % bs;
+        for (int i = lane; i < hd; i += 32) k_cache[page_row * hd + i] = from_f<TO>(v[i]);
+        const TI* vs = row_base + (size_t)t * ld + (size_t)(H + G) * hd + (size_t)kh * hdv;
+        for (int i = lane; i < hdv; i += 32) v_cache[page_row * hdv + i] = from_f<TO>(to_f<TI>(vs[i]));
+    }
+}
+
+RLLM_API int rllm_head_norm_rope_store(const void* rows, int in_dt, long long ld, const float* q_w, const float* k_w,
+                                       const void* cs_table, int rot, int pairs, const int* slots, void* q_out,
+                                       void* k_cache, void* v_cache, int out_dt, int n, int H, int G, int hd, int hdv,
+                                       int bs, float eps, int has_kv, int write_kv, long long n_slots, int* err,
+                                       cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (H <= 0 || G <= 0 || hd <= 0 || hdv <= 0 || rot < 0 || rot > hd || (rot & 1) || bs <= 0 || (rot && !cs_table) ||
+        ld < (long long)H * hd + (has_kv ? (long long)G * (hd + hdv) : 0))
+        return (int)cudaErrorInvalidValue;
+    const int ns = (int)(n_slots > 0x7fffffffLL ? 0x7fffffffLL : n_slots);
+    const dim3 grid(n, (H + (has_kv ? G : 0) + 3) / 4);
+    const size_t smem = (size_t)4 * hd * sizeof(float);
+#define LAUNCH(TI, TO)                                                                                           \
+    return rllm_launch(head_norm_rope_store_kernel<TI, TO>, grid, dim3(128), smem, stream, (const TI*)rows, ld,   \
+                       q_w, k_w, (const float2*)cs_table, rot, pairs, slots, (TO*)q_out, (TO*)k_cache,            \
+                       (TO*)v_cache, H, G, hd, hdv, bs, eps, has_kv, write_kv, ns, err)
+    if (in_dt == RLLM_F32 && out_dt == RLLM_F32) { LAUNCH(float, float); }
+    if (in_dt == RLLM_F32 && out_dt == RLLM_BF16) { LAUNCH(float, bf16); }
+    if (in_dt == RLLM_BF16 && out_dt == RLLM_BF16) { LAUNCH(bf16, bf16); }
+    return (int)cudaErrorInvalidValue;
+#undef LAUNCH
+}
+
+// ------------------------------------------------------------------ a norm on an output, joined, and the next norm
+// One block per row: x[t] += y[t] / rms(y[t]) * w_out, then out[t] = x[t] / rms(x[t]) * w_next in the
+// activation type.  The new row of x stays in shared memory between the two halves.
+template <typename TY, typename TO>
+__global__ void __launch_bounds__(256)
+join_norm_rows_kernel(const TY* y, long long ld_y, const float* __restrict__ w_out, float eps_out, float* x,
+                      const float* __restrict__ w_next, float eps_next, TO* out, int d) {
+    extern __shared__ float row[];
+    __shared__ float red[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t t = blockIdx.x;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float v = to_f<TY>(y[t * ld_y + i]);
+        row[i] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float rs = 1.0f / sqrtf(ss / (float)d + eps_out);
+    float s2 = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float v = x[t * d + i] + row[i] * rs * w_out[i];
+        x[t * d + i] = v;
+        row[i] = v;
+        s2 += v * v;
+    }
+    s2 = block_sum(s2, red);
+    const float r2 = 1.0f / sqrtf(s2 / (float)d + eps_next);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) out[t * d + i] = from_f<TO>(row[i] * r2 * w_next[i]);
+}
+
+RLLM_API int rllm_join_norm_rows(const void* y, int y_dt, long long ld_y, const float* w_out, float eps_out, float* x,
+                                 const float* w_next, float eps_next, void* out, int out_dt, int n, int d,
+                                 cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (d <= 0 || ld_y < d || !w_out || !w_next || !x || !out) return (int)cudaErrorInvalidValue;
+    const size_t smem = (size_t)d * sizeof(float);
+    if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
+    const dim3 block(d >= 2048 ? 256 : 128);
+#define LAUNCH(TY, TO)                                                                                          \
+    return rllm_launch(join_norm_rows_kernel<TY, TO>, dim3(n), block, smem, stream, (const TY*)y, ld_y, w_out,   \
+                       eps_out, x, w_next, eps_next, (TO*)out, d)
+    if (y_dt == RLLM_F32 && out_dt == RLLM_F32) { LAUNCH(float, float); }
+    if (y_dt == RLLM_F32 && out_dt == RLLM_BF16) { LAUNCH(float, bf16); }
+    if (y_dt == RLLM_BF16 && out_dt == RLLM_BF16) { LAUNCH(bf16, bf16); }
+    return (int)cudaErrorInvalidValue;
+#undef LAUNCH
+}
+
+RLLM_PACKED(rllm_head_norm_rope_store)
+RLLM_PACKED(rllm_join_norm_rows)
 RLLM_PACKED(rllm_masked_softmax_rows)
 RLLM_PACKED(rllm_norm_rows)
 RLLM_PACKED(rllm_rope_unitnorm_store)

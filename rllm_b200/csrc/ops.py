@@ -344,13 +344,16 @@ def qk_norm_rope_store(qkv, q_norm_w, k_norm_w, inv_freq, positions, slots, q_ou
 # ------------------------------------------------------------------ attention
 
 def paged_attention_generic(q, k_cache, v_cache, out, positions, seq_ids, block_table, H, K, hd,
-                            block_size, scale, window=0, keep_first=0, v_head_dim=None, chunk=0, softcap=0.0):
+                            block_size, scale, window=0, keep_first=0, v_head_dim=None, chunk=0, softcap=0.0,
+                            sink=None):
     """Plain paged causal attention; q [n, H*hd], out [n, H*hdv], caches [pages, K, block_size, hd] and
     [pages, K, block_size, hdv] (hdv = v_head_dim, hd by default).  keep_first: the first keys of a
     request stay visible when the window has passed them.  chunk: a token sees only the keys of its
     own run of that many positions (counted from 0).  softcap: scores go through cap * tanh(s / cap).
-    `v_cache is k_cache` with hdv < hd: the values are the first hdv entries of the key rows."""
-    _need_cuda(q, k_cache, v_cache, out, positions, seq_ids, block_table)
+    `v_cache is k_cache` with hdv < hd: the values are the first hdv entries of the key rows.
+    sink (float32 [H]): exp(sink[h]) joins the softmax's denominator of head h, with no key and no value."""
+    _need_cuda(q, k_cache, v_cache, out, positions, seq_ids, block_table, sink)
+    assert sink is None or (sink.dtype == torch.float32 and sink.numel() == H and sink.is_contiguous())
     _need_contig(q=q, k_cache=k_cache, v_cache=v_cache, out=out, positions=positions, seq_ids=seq_ids)
     n = q.shape[0]
     hdv = hd if not v_head_dim else int(v_head_dim)
@@ -368,7 +371,7 @@ def paged_attention_generic(q, k_cache, v_cache, out, positions, seq_ids, block_
         c_int(_code(out)), _ptr(positions), _ptr(seq_ids), _ptr(block_table), c_int(block_table.stride(0)),
         c_int(n), c_int(H), c_int(K), c_int(hd), c_int(hdv), c_int(block_size), c_float(scale), c_int(window),
         c_int(keep_first), c_int(min(k_cache.shape[0], 0x7fffffff)), _ptr(error_word(q.device)), c_int(chunk),
-        c_float(softcap), c_int(v_ld), _stream()),
+        c_float(softcap), c_int(v_ld), _ptr(sink), _stream()),
         "paged_attention_generic")
     return out
 
@@ -416,6 +419,51 @@ def rope_unitnorm_store(rows, cs_table, rot, cs_mult, slots, q_out, k_cache, v_c
         c_int(1 if write_kv else 0), c_longlong(k_cache.shape[0] * block_size), _ptr(error_word(rows.device)),
         _stream()), "rope_unitnorm_store")
     return q_out
+
+
+def head_norm_rope_store(rows, q_norm_w, k_norm_w, cs_table, rot, pairs, slots, q_out, k_cache, v_cache, H, G, hd, hdv,
+                         block_size, eps, has_kv=True, write_kv=True):
+    """rows [n, H*hd (+ G*hd + G*hdv when has_kv)] -> per query and key head: RMS norm with a weight of hd
+    entries (None: no norm), then the first `rot` entries rotated by the angles of cs_table [n, rot/2, 2]
+    (pairs (2i, 2i+1) when `pairs`, else (i, i + rot/2)); queries to q_out, keys and values (heads of hdv
+    entries) into the paged cache.  See headwise.cu."""
+    _need_cuda(rows, q_norm_w, k_norm_w, cs_table, slots, q_out, k_cache, v_cache)
+    _need_contig(q_out=q_out, k_cache=k_cache, v_cache=v_cache, slots=slots)
+    _rows2d(rows, "rows")
+    n = rows.shape[0]
+    assert rows.shape[1] == H * hd + (G * (hd + hdv) if has_kv else 0) and q_out.shape == (n, H * hd)
+    assert slots.dtype == torch.int32 and slots.numel() == n
+    assert k_cache.shape[1:] == (G, block_size, hd) and v_cache.shape[1:] == (G, block_size, hdv)
+    assert k_cache.dtype == v_cache.dtype == q_out.dtype
+    for w in (q_norm_w, k_norm_w):
+        assert w is None or (w.dtype == torch.float32 and w.numel() == hd and w.is_contiguous())
+    assert rot == 0 or (cs_table.dtype == torch.float32 and cs_table.shape == (n, rot // 2, 2) and cs_table.is_contiguous())
+    _check(core().rllm_head_norm_rope_store(
+        _ptr(rows), c_int(_code(rows)), c_longlong(rows.stride(0)), _ptr(q_norm_w), _ptr(k_norm_w),
+        _ptr(cs_table if rot else None), c_int(rot), c_int(1 if pairs else 0), _ptr(slots), _ptr(q_out), _ptr(k_cache),
+        _ptr(v_cache), c_int(_code(q_out)), c_int(n), c_int(H), c_int(G), c_int(hd), c_int(hdv), c_int(block_size),
+        c_float(eps), c_int(1 if has_kv else 0), c_int(1 if (write_kv and has_kv) else 0),
+        c_longlong(k_cache.shape[0] * block_size), _ptr(error_word(rows.device)), _stream()), "head_norm_rope_store")
+    return q_out
+
+
+def join_norm_rows(y, w_out, eps_out, x, w_next, eps_next, out):
+    """x += y / rms(y) * w_out (x: the float32 stream, in place), out = x / rms(x) * w_next in out's type:
+    one kernel for the norm on a sublayer's output and the norm in front of the next sublayer.  Rows
+    too long for the kernel's shared memory take the two kernels it stands for."""
+    _need_cuda(y, w_out, x, w_next, out)
+    _need_contig(x=x, out=out, w_out=w_out, w_next=w_next)
+    _rows2d(y, "y")
+    n, d = x.shape
+    assert x.dtype == torch.float32 and y.shape == (n, d) and out.shape == (n, d)
+    assert w_out.dtype == w_next.dtype == torch.float32 and w_out.numel() == w_next.numel() == d
+    if d * 4 > 48 * 1024:
+        norm_rows(y, w_out, eps_out, x=x, add=True)
+        return add_rms_norm(x, None, w_next, out, eps_next)
+    _check(core().rllm_join_norm_rows(_ptr(y), c_int(_code(y)), c_longlong(y.stride(0)), _ptr(w_out), c_float(eps_out),
+                                      _ptr(x), _ptr(w_next), c_float(eps_next), _ptr(out), c_int(_code(out)), c_int(n),
+                                      c_int(d), _stream()), "join_norm_rows")
+    return out
 
 
 def latent_rope_store(q, kv, kv_norm_w, cs_table, cs_mult, slots, q_att, cache, H, dq, r, rank, block_size, eps,
@@ -696,6 +744,147 @@ def wkv(r, k, v, wraw, g, w0, u, norm_w, eps, state, prev_off, h, cu_q, slots, o
     if sg is not None:
         global _launches
         _launches += 2                         # the local pass and the combine kernel
+    return out
+
+
+def retention_state_floats(H: int, dk: int, dv: int) -> int:
+    """Floats of a request's retention state (each head's dk x dv state padded to the kernel's tile and in
+    its threads' order; recurrent.cu).  No device needed."""
+    dkmax = 32 if dk <= 32 else 64 if dk <= 64 else 128 if dk <= 128 else 256
+    threads = ((dv + 1) // 2 * 8 + 31) // 32 * 32
+    return H * dkmax * (threads // 8 * 2)
+
+
+GATES = {None: 0, "none": 0, "silu": 1, "sigmoid": 2}
+
+
+def retention(rows, q_off, k_off, v_off, g_off, cs_table, rot, pairs, key_scale, decay, eps, state, cu_q, slots, out,
+              n_requests, H, dk, dv, gate="silu", segments=None):
+    """Linear attention with a fixed decay per head over each request's tokens, its state in state[slot];
+    see recurrent.cu.  rows: float32 [n, ...] holding q, k ([H*dk] each) and v, gate ([H*dv] each) at the
+    given column offsets; decay float32 [H]; out activation type [n, H*dv].  segments: the step's
+    TimeSegments or None."""
+    _need_cuda(rows, cs_table, decay, state, cu_q, slots, out)
+    _rows2d(rows, "rows")
+    _need_contig(out=out, decay=decay)
+    n = out.shape[0]
+    assert rows.dtype == torch.float32 and rows.shape[0] == n and out.shape == (n, H * dv)
+    assert decay.dtype == torch.float32 and decay.numel() == H
+    assert max(q_off, k_off) + H * dk <= rows.shape[1] and v_off + H * dv <= rows.shape[1]
+    assert gate in (None, "none") or g_off + H * dv <= rows.shape[1]
+    assert rot == 0 or (cs_table.dtype == torch.float32 and cs_table.shape == (n, rot // 2, 2) and cs_table.is_contiguous())
+    if dk > 256 or dv > 256:
+        raise KernelError(f"head sizes {dk} x {dv} exceed the retention kernel's limit of 256")
+    st = _state2d(state)
+    per_head = retention_state_floats(1, dk, dv)
+    assert H * per_head <= st.shape[1]
+    sg = segments
+    carry = torch.empty((sg.n_items, H, per_head), dtype=torch.float32, device=out.device) if sg is not None else None
+    base = rows.data_ptr()
+    col = lambda off: c_void_p(base + 4 * off)
+    _ptr(rows)                                 # a traced launch keeps the rows alive
+    _check(_lib("recur").rllm_retention(
+        col(q_off), col(k_off), col(v_off), col(g_off) if GATES[gate] else c_void_p(0), c_longlong(rows.stride(0)),
+        _ptr(cs_table if rot else None), c_int(rot), c_int(1 if pairs else 0), c_float(key_scale), _ptr(decay),
+        c_float(eps), _ptr(st), c_longlong(st.stride(0)), _ptr(cu_q), _ptr(slots), _ptr(out), c_int(_code(out)),
+        c_int(n_requests), c_int(H), c_int(dk), c_int(dv), c_int(GATES[gate]),
+        _ptr(sg.t0 if sg else None), _ptr(sg.t1 if sg else None), _ptr(sg.req if sg else None),
+        _ptr(sg.flags if sg else None), _ptr(sg.item0 if sg else None), _ptr(sg.items if sg else None),
+        c_int(sg.n_items if sg else 0), _ptr(carry), _stream()), "retention")
+    if sg is not None:
+        global _launches
+        _launches += 2                         # the local pass and the combine kernel
+    return out
+
+
+# ------------------------------------------------------------------ routed experts (moe.cu)
+
+def moe_route(logits, correction, idx, weight, E, top_k, n_groups=1, keep_groups=1, group_best=2, score="sigmoid",
+              normalize=True, weight_eps=0.0, route_scale=1.0):
+    """The router's choice per token from float32 logits (the first E columns of `logits`): idx int32
+    [n, top_k], weight float32 [n, top_k]; see moe.cu."""
+    _need_cuda(logits, correction, idx, weight)
+    _rows2d(logits, "logits")
+    _need_contig(idx=idx, weight=weight, correction=correction)
+    n = logits.shape[0]
+    assert logits.dtype == torch.float32 and logits.shape[1] >= E
+    assert idx.dtype == torch.int32 and idx.shape == (n, top_k) and weight.dtype == torch.float32 and weight.shape == (n, top_k)
+    assert correction is None or (correction.dtype == torch.float32 and correction.numel() == E)
+    if score not in ("sigmoid", "softmax"):
+        raise KernelError(f"moe_route: score {score!r} is not known")
+    if E > 1024:
+        raise KernelError(f"{E} experts exceed the router kernel's limit of 1024")
+    _check(_lib("moe").rllm_moe_route(_ptr(logits), c_longlong(logits.stride(0)), _ptr(correction), _ptr(idx), _ptr(weight),
+                                      c_int(n), c_int(E), c_int(top_k), c_int(n_groups), c_int(keep_groups),
+                                      c_int(group_best), c_int(1 if score == "softmax" else 0), c_int(1 if normalize else 0),
+                                      c_float(weight_eps), c_float(route_scale), _stream()), "moe_route")
+    return idx, weight
+
+
+def moe_pairs_gate_up(h, w_gu, idx, act, glu=(0.0, 1.0, 0.0)):
+    """act[t * top_k + j] = glu(Wg[e] h[t], Wu[e] h[t]) with e = idx[t, j]; w_gu [E, 2F, d] (gate rows, then up
+    rows); h, w_gu, act of one type."""
+    _need_cuda(h, w_gu, idx, act)
+    _need_contig(h=h, w_gu=w_gu, idx=idx, act=act)
+    n, d = h.shape
+    top_k, F = idx.shape[1], act.shape[1]
+    assert w_gu.shape[1:] == (2 * F, d) and act.shape == (n * top_k, F) and h.dtype == w_gu.dtype == act.dtype
+    _check(_lib("moe").rllm_moe_pairs_gate_up(_ptr(h), _ptr(w_gu), c_int(_code(h)), _ptr(idx), _ptr(act), c_int(n),
+                                              c_int(top_k), c_int(d), c_int(F), c_float(glu[0]), c_float(glu[1]),
+                                              c_float(glu[2]), _stream()), "moe_pairs_gate_up")
+    return act
+
+
+def moe_pairs_down(act, w_down, idx, weight, out, shared=None, gate=None):
+    """out[t] = sum_j weight[t, j] * Wd[idx[t, j]] act[t * top_k + j] (+ shared[t] * sigmoid(gate[t]));
+    w_down [E, d, F]; out, shared float32 [n, d]; gate: float32 logits, one per token (a column)."""
+    _need_cuda(act, w_down, idx, weight, out, shared, gate)
+    _need_contig(act=act, w_down=w_down, idx=idx, weight=weight, out=out, shared=shared)
+    n, d = out.shape
+    top_k, F = idx.shape[1], act.shape[1]
+    assert w_down.shape[1:] == (d, F) and act.shape == (n * top_k, F) and act.dtype == w_down.dtype
+    assert out.dtype == torch.float32 and (shared is None or (shared.dtype == torch.float32 and shared.shape == (n, d)))
+    assert gate is None or (gate.dtype == torch.float32 and gate.shape[0] == n)
+    if top_k * F * 4 > 96 * 1024:
+        raise KernelError("moe_pairs_down: top_k * expert size exceeds the kernel's shared memory")
+    _check(_lib("moe").rllm_moe_pairs_down(_ptr(act), _ptr(w_down), c_int(_code(act)), _ptr(idx), _ptr(weight), _ptr(out),
+                                           _ptr(shared), _ptr(gate), c_longlong(gate.stride(0) if gate is not None else 0),
+                                           c_int(n), c_int(top_k), c_int(d), c_int(F), _stream()), "moe_pairs_down")
+    return out
+
+
+def moe_sort(idx, E):
+    """(offsets int32 [E + 1], place int32 [pairs]): the pairs of idx [n, top_k] in expert order (stable)."""
+    _need_cuda(idx)
+    _need_contig(idx=idx)
+    offsets = torch.empty(E + 1, dtype=torch.int32, device=idx.device)
+    place = torch.empty(idx.numel(), dtype=torch.int32, device=idx.device)
+    _check(_lib("moe").rllm_moe_sort(_ptr(idx), c_int(idx.numel()), c_int(E), _ptr(offsets), _ptr(place), _stream()),
+           "moe_sort")
+    return offsets, place
+
+
+def moe_gather_rows(h, place, rows, top_k):
+    """rows[place[p]] = h[p // top_k] for every pair p."""
+    _need_cuda(h, place, rows)
+    _need_contig(h=h, place=place, rows=rows)
+    assert rows.shape == (place.numel(), h.shape[1]) and rows.dtype == h.dtype
+    _check(_lib("moe").rllm_moe_gather_rows(_ptr(h), c_int(_code(h)), _ptr(place), _ptr(rows), c_int(place.numel()),
+                                            c_int(top_k), c_int(h.shape[1]), _stream()), "moe_gather_rows")
+    return rows
+
+
+def moe_combine(y, place, weight, out, shared=None, gate=None):
+    """out[t] = sum_j weight[t, j] * y[place[t * top_k + j]] (+ shared[t] * sigmoid(gate[t])), float32."""
+    _need_cuda(y, place, weight, out, shared, gate)
+    _need_contig(y=y, place=place, weight=weight, out=out, shared=shared)
+    n, d = out.shape
+    top_k = weight.shape[1]
+    assert y.dtype == out.dtype == torch.float32 and y.shape == (n * top_k, d)
+    assert shared is None or (shared.dtype == torch.float32 and shared.shape == (n, d))
+    _check(_lib("moe").rllm_moe_combine(_ptr(y), _ptr(place), _ptr(weight), _ptr(out), _ptr(shared), _ptr(gate),
+                                        c_longlong(gate.stride(0) if gate is not None else 0), c_int(n), c_int(top_k),
+                                        c_int(d), _stream()), "moe_combine")
     return out
 
 
@@ -1552,16 +1741,16 @@ def shared_kv_attention(q, cache, out, ctx, block_table, H, hd, hdv, block_size,
 
 
 def paged_attention(q, k_cache, v_cache, out, ctx, block_table, H, K, hd, block_size, scale, window=0,
-                    keep_first=0, v_head_dim=None, chunk=0, softcap=0.0):
+                    keep_first=0, v_head_dim=None, chunk=0, softcap=0.0, sink=None):
     """Attention of the step's tokens over the paged cache; chooses the kernel by element type,
     head size and the shape of the step (`ctx`: the step's StepContext).  float32, head sizes
     other than 64 and 128 and value heads of another size than the key heads take the plain kernel;
     windows that keep the first keys take the mma.sync kernels, not the tcgen05 one."""
     hdv = hd if not v_head_dim else int(v_head_dim)
     keep_first = keep_first if window else 0
-    if q.dtype != torch.bfloat16 or hd not in FLASH_HEAD_DIMS or hdv != hd:
+    if q.dtype != torch.bfloat16 or hd not in FLASH_HEAD_DIMS or hdv != hd or sink is not None:
         return paged_attention_generic(q, k_cache, v_cache, out, ctx.positions, ctx.seq_ids, block_table,
-                                       H, K, hd, block_size, scale, window, keep_first, hdv, chunk, softcap)
+                                       H, K, hd, block_size, scale, window, keep_first, hdv, chunk, softcap, sink)
     key = (H // K, window, chunk)
     plan = ctx.plans.get(key)
     if plan is None:

@@ -1,6 +1,6 @@
 // Layers that carry a fixed-size state per request from token to token: the selective scan
-// (Mamba) with its short causal convolution, and RWKV-style time mixing with a data-dependent
-// decay.  A request's state lives in a slot of the state array (float32), is read at the start of
+// (Mamba) with its short causal convolution, RWKV-style time mixing with a data-dependent
+// decay, and retention (linear attention with a fixed decay per head).  A request's state lives in a slot of the state array (float32), is read at the start of
 // the request's tokens in this step and written back at their end; the tokens of a request are
 // contiguous in the flat batch (cu_q) and in order.  Everything that enters a recurrence (step
 // sizes, decays, their exponentials, gates, unit norms, the state itself) is float32 with accurate
@@ -14,6 +14,7 @@
 //           or 256; rllm_wkv_state_floats) in the order in which the WKV kernel's threads hold it, so
 //           that a step reads and writes it in whole lines: value (register, thread) at register *
 //           threads + thread; then the previous token's input [width].  Nothing else reads S.
+//   retention:  S of every head, DKMAX * dvp floats a head, in the retention kernel's thread order.
 #include "common.cuh"
 #include <math.h>
 
@@ -687,7 +688,288 @@ RLLM_API long long rllm_wkv_state_floats(int H, int D) {
     return (long long)H * dmax * dmax;
 }
 
+// ------------------------------------------------------------------ retention: linear attention with a fixed decay per head
+// One block per (request or segment, head).  Per token, with q, k the head's rows of the projections
+// (dk entries) after their rotation, k also multiplied by key_scale, v the head's values (dv entries)
+// and c the head's decay:
+//   S[i][j] = c * S[i][j] + k[i] * v[j];     o[j] = sum_i q[i] * S[i][j]        (S after the update)
+// then o is divided by its root mean square over the head (eps inside the root), multiplied by
+// silu(gate) and stored in the activation type.  The rotation turns the first `rot` entries of q and
+// k by the token's angles (pairs (i, i + rot/2), or (2i, 2i + 1) when `pairs`) and is done here, on the
+// chunk in shared memory, so q and k come in as projected.
+// A thread owns an eighth of the key channels (DKMAX / 8, in runs of four that interleave with the
+// other seven lanes' so that their float4 reads of q and k fall side by side) of two neighbouring value
+// channels of the state, in registers; the RET_PARTS lanes that share a pair of columns add their
+// partial sums in a fixed butterfly.  The block has 8 * ceil(dv / 2) threads (rounded up to whole
+// warps).  Tokens are taken RET_TOK at a time through two buffers of shared memory filled by cp.async:
+// the next chunk is on its way while this one is worked through.  The state of a head lies in the slot
+// in the threads' own order, DKMAX * dvp floats a head (dvp: dv rounded up to a multiple of 8;
+// rllm_retention_state_floats).
+// Long portions are cut along time as for the WKV kernel (TimeSegments): S_end = c^len * S_start +
+// (end state from a zero start); the power is worked out in double precision.
+#define RET_TOK 16
+#define RET_PARTS 8
+
+__device__ __forceinline__ void ret_cp_async4(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src));
+}
+
+template <typename TA, int DKMAX, int PASS, int MAXT>
+__global__ void __launch_bounds__(MAXT)
+retention_kernel(const float* qp, const float* kp, const float* vp, const float* gp, long long ld,
+                 const float2* cs_table, int rot, int pairs, float key_scale, const float* __restrict__ decay, float eps,
+                 float* state, long long slot_stride, const int* __restrict__ cu_q, const int* __restrict__ slots,
+                 TA* out, int H, int dk, int dv, int gate, const TimeSegments seg) {
+    constexpr int IPT = DKMAX / RET_PARTS;
+    extern __shared__ __align__(16) float sm_ret[];
+    const int NT = blockDim.x, dvp = NT / RET_PARTS * 2;
+    const int stage = RET_TOK * (2 * DKMAX + 2 * dvp);
+    float* s_o = sm_ret + 2 * stage;                      // [RET_TOK][dvp]
+    const int tid = threadIdx.x, j0 = 2 * (tid / RET_PARTS), part = tid % RET_PARTS;
+    const int head = blockIdx.x, item = blockIdx.y;
+    const float c = decay[head];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int r = PASS == 0 ? item : seg.req[item];
+    const int t0 = PASS == 0 ? cu_q[r] : seg.t0[item], t1 = PASS == 0 ? cu_q[r + 1] : seg.t1[item];
+    const bool first = PASS == 0 || (seg.flags[item] & 1), last = PASS == 0 || (seg.flags[item] & 2);
+    if (PASS == 1 && last) return;                        // its end state comes out of pass 2
+    const size_t per_head = (size_t)DKMAX * dvp;
+    float* Sg = state + (size_t)slots[r] * slot_stride + (size_t)head * per_head;
+    float S0[IPT], S1[IPT];
+    {
+        const int src = first ? item + seg.req_items[r] - 1 : item - 1;
+        const float* from = (first && last) ? Sg : seg.carry + ((size_t)src * H + head) * per_head;
+#pragma unroll
+        for (int ii = 0; ii < IPT; ++ii) {
+            S0[ii] = PASS == 1 ? 0.f : from[(size_t)(2 * ii) * NT + tid];
+            S1[ii] = PASS == 1 ? 0.f : from[(size_t)(2 * ii + 1) * NT + tid];
+        }
+    }
+    const size_t qcol = (size_t)head * dk, vcol = (size_t)head * dv;
+    // a chunk's q, k (rows of DKMAX, zeros beyond dk), v and gate (rows of dvp) into a buffer
+    auto issue = [&](int tb, int buf) {
+        float* base = sm_ret + buf * stage;
+        const int nt = min(RET_TOK, t1 - tb);
+        for (int e = tid; e < 2 * RET_TOK * DKMAX; e += NT) {
+            const int arr = e / (RET_TOK * DKMAX), rem = e % (RET_TOK * DKMAX), tt = rem / DKMAX, cc = rem % DKMAX;
+            if (tt < nt && cc < dk) ret_cp_async4(base + e, (arr ? kp : qp) + (size_t)(tb + tt) * ld + qcol + cc);
+            else base[e] = 0.f;
+        }
+        float* vb = base + 2 * RET_TOK * DKMAX;
+        for (int e = tid; e < 2 * RET_TOK * dvp; e += NT) {
+            const int arr = e / (RET_TOK * dvp), rem = e % (RET_TOK * dvp), tt = rem / dvp, cc = rem % dvp;
+            if (tt < nt && cc < dv && (arr == 0 || gp)) ret_cp_async4(vb + e, (arr ? gp : vp) + (size_t)(tb + tt) * ld + vcol + cc);
+            else vb[e] = 0.f;
+        }
+        asm volatile("cp.async.commit_group;\n" ::);
+    };
+    const int warp = tid >> 5, lane = tid & 31, n_warps = NT >> 5;
+    const int half = rot >> 1;
+    if (t0 < t1) issue(t0, 0);
+    int buf = 0;
+    for (int tb = t0; tb < t1; tb += RET_TOK, buf ^= 1) {
+        const int nt = min(RET_TOK, t1 - tb);
+        const bool more = tb + RET_TOK < t1;
+        if (more) {
+            issue(tb + RET_TOK, buf ^ 1);
+            asm volatile("cp.async.wait_group 1;\n" ::);
+        } else {
+            asm volatile("cp.async.wait_group 0;\n" ::);
+        }
+        __syncthreads();
+        float* s_q = sm_ret + buf * stage;
+        float* s_k = s_q + RET_TOK * DKMAX;
+        float* s_v = s_k + RET_TOK * DKMAX;
+        float* s_g = s_v + RET_TOK * dvp;
+        // the rotation of q and k, and the keys' scale
+        for (int e = tid; e < 2 * nt * half; e += NT) {
+            const int arr = e / (nt * half), rem = e % (nt * half), tt = rem / half, i = rem % half;
+            const float2 a = cs_table[(size_t)(tb + tt) * half + i];
+            float* row = (arr ? s_k : s_q) + tt * DKMAX;
+            const int iu = pairs ? 2 * i : i, iv = pairs ? 2 * i + 1 : i + half;
+            const float u = row[iu], x = row[iv];
+            row[iu] = u * a.x - x * a.y;
+            row[iv] = x * a.x + u * a.y;
+        }
+        __syncthreads();
+        if (key_scale != 1.f)
+            for (int e = tid; e < nt * DKMAX; e += NT) s_k[e] *= key_scale;
+        __syncthreads();
+        auto token = [&](int tt) {
+            const float2 vj = *reinterpret_cast<const float2*>(s_v + tt * dvp + j0);
+            const float4* q4 = reinterpret_cast<const float4*>(s_q + tt * DKMAX);
+            const float4* k4 = reinterpret_cast<const float4*>(s_k + tt * DKMAX);
+            float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+#pragma unroll
+            for (int q = 0; q < IPT / 4; ++q) {
+                const float4 qq = q4[part + RET_PARTS * q], kk = k4[part + RET_PARTS * q];
+#define RET_STEP(Q, K, I, A, B)                                                  \
+                S0[I] = c * S0[I] + K * vj.x; S1[I] = c * S1[I] + K * vj.y;      \
+                if (PASS != 1) { A += Q * S0[I]; B += Q * S1[I]; }
+                RET_STEP(qq.x, kk.x, 4 * q, a0, b0)
+                RET_STEP(qq.y, kk.y, 4 * q + 1, a1, b1)
+                RET_STEP(qq.z, kk.z, 4 * q + 2, a0, b0)
+                RET_STEP(qq.w, kk.w, 4 * q + 3, a1, b1)
+#undef RET_STEP
+            }
+            if (PASS == 1) return;
+            float oa = a0 + a1, ob = b0 + b1;
+#pragma unroll
+            for (int m = 1; m < RET_PARTS; m <<= 1) {
+                oa += __shfl_xor_sync(0xffffffffu, oa, m);
+                ob += __shfl_xor_sync(0xffffffffu, ob, m);
+            }
+            if (part == 0) *reinterpret_cast<float2*>(s_o + tt * dvp + j0) = make_float2(oa, ob);
+        };
+        if (nt == RET_TOK) {
+#pragma unroll 2
+            for (int tt = 0; tt < RET_TOK; ++tt) token(tt);
+        } else {
+            for (int tt = 0; tt < nt; ++tt) token(tt);
+        }
+        __syncthreads();
+        for (int tt = warp; PASS != 1 && tt < nt; tt += n_warps) {
+            float ss = 0.f;
+            for (int i = lane; i < dv; i += 32) ss += s_o[tt * dvp + i] * s_o[tt * dvp + i];
+            const float rs = 1.0f / sqrtf(warp_sum(ss) / (float)dv + eps);
+            for (int i = lane; i < dv; i += 32) {
+                float v = s_o[tt * dvp + i] * rs;
+                if (gate == 1) v *= silu_f(s_g[tt * dvp + i]);
+                else if (gate == 2) v *= 1.0f / (1.0f + expf(-s_g[tt * dvp + i]));
+                out[(size_t)(tb + tt) * H * dv + vcol + i] = from_f<TA>(v);
+            }
+        }
+        __syncthreads();                                  // everyone is done with this buffer and with s_o
+    }
+    float* to = PASS == 1 ? seg.carry + ((size_t)item * H + head) * per_head : Sg;
+    if (PASS != 1 && !last) return;
+#pragma unroll
+    for (int ii = 0; ii < IPT; ++ii) {
+        to[(size_t)(2 * ii) * NT + tid] = S0[ii];
+        to[(size_t)(2 * ii + 1) * NT + tid] = S1[ii];
+    }
+}
+
+// Between the passes: a request's segments in order, S_end = c^len * S_start + local end state, in place.
+template <int DKMAX>
+__global__ void retention_combine_kernel(const float* state, long long slot_stride, const int* __restrict__ slots,
+                                         const float* __restrict__ decay, int H, const TimeSegments seg) {
+    constexpr int IPT = DKMAX / RET_PARTS;
+    pdl_wait();
+    pdl_launch_dependents();
+    const int tid = threadIdx.x, NT = blockDim.x, head = blockIdx.x, r = blockIdx.y;
+    const int n = seg.req_items[r], item0 = seg.req_item0[r];
+    if (n < 2) return;
+    const size_t per_head = (size_t)DKMAX * (NT / RET_PARTS * 2);
+    const float* Sg = state + (size_t)slots[r] * slot_stride + (size_t)head * per_head;
+    float S[2 * IPT];
+    float* keep = seg.carry + ((size_t)(item0 + n - 1) * H + head) * per_head;    // the start state, for pass 2
+#pragma unroll
+    for (int ii = 0; ii < 2 * IPT; ++ii) {
+        S[ii] = Sg[(size_t)ii * NT + tid];
+        keep[(size_t)ii * NT + tid] = S[ii];
+    }
+    const double c = (double)decay[head];
+    for (int it = item0; it < item0 + n - 1; ++it) {
+        float* C = seg.carry + ((size_t)it * H + head) * per_head;
+        const float w = (float)pow(c, (double)(seg.t1[it] - seg.t0[it]));
+#pragma unroll
+        for (int ii = 0; ii < 2 * IPT; ++ii) {
+            S[ii] = w * S[ii] + C[(size_t)ii * NT + tid];
+            C[(size_t)ii * NT + tid] = S[ii];
+        }
+    }
+}
+
+static inline int ret_dkmax(int dk) { return dk <= 32 ? 32 : dk <= 64 ? 64 : dk <= 128 ? 128 : 256; }
+static inline int ret_threads(int dv) { return ((dv + 1) / 2 * RET_PARTS + 31) / 32 * 32; }
+
+template <typename TA, int DKMAX, int PASS, int MAXT>
+static int launch_retention_pass(dim3 grid, int threads, size_t smem, cudaStream_t stream, const float* qp,
+                                 const float* kp, const float* vp, const float* gp, long long ld, const void* cs_table,
+                                 int rot, int pairs, float key_scale, const float* decay, float eps, float* state,
+                                 long long slot_stride, const int* cu_q, const int* slots, void* out, int H, int dk, int dv,
+                                 int gate, const TimeSegments& seg) {
+    if (smem > 48 * 1024) {
+        static size_t raised = 0;                         // per instantiation: more dynamic shared memory than the default
+        if (smem > raised) {
+            cudaError_t e = cudaFuncSetAttribute(retention_kernel<TA, DKMAX, PASS, MAXT>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+            raised = smem;
+        }
+    }
+    return rllm_launch(retention_kernel<TA, DKMAX, PASS, MAXT>, grid, dim3(threads), smem, stream, qp, kp, vp, gp, ld,
+                       (const float2*)cs_table, rot, pairs, key_scale, decay, eps, state, slot_stride, cu_q, slots,
+                       (TA*)out, H, dk, dv, gate, seg);
+}
+
+template <typename TA, int DKMAX, int MAXT>
+static int launch_retention(int n_requests, int threads, size_t smem, cudaStream_t stream, const float* qp, const float* kp,
+                            const float* vp, const float* gp, long long ld, const void* cs_table, int rot, int pairs,
+                            float key_scale, const float* decay, float eps, float* state, long long slot_stride,
+                            const int* cu_q, const int* slots, void* out, int H, int dk, int dv, int gate,
+                            const TimeSegments& seg) {
+#define RET_ARGS qp, kp, vp, gp, ld, cs_table, rot, pairs, key_scale, decay, eps, state, slot_stride, cu_q, slots, out, H, dk, dv, gate, seg
+    if (seg.n_items <= 0)
+        return launch_retention_pass<TA, DKMAX, 0, MAXT>(dim3(H, n_requests), threads, smem, stream, RET_ARGS);
+    int st = launch_retention_pass<TA, DKMAX, 1, MAXT>(dim3(H, seg.n_items), threads, smem, stream, RET_ARGS);
+    if (st) return st;
+    st = rllm_launch(retention_combine_kernel<DKMAX>, dim3(H, n_requests), dim3(threads), 0, stream, (const float*)state,
+                     slot_stride, slots, decay, H, seg);
+    if (st) return st;
+    return launch_retention_pass<TA, DKMAX, 2, MAXT>(dim3(H, seg.n_items), threads, smem, stream, RET_ARGS);
+#undef RET_ARGS
+}
+
+// q, k [n, H*dk], v, gate [n, H*dv]: float32 columns of one projection (rows ld apart); gate_kind 0: none
+// (gp may be null), 1: silu, 2: sigmoid.  carry needs n_items * H * DKMAX * dvp floats.
+RLLM_API int rllm_retention(const float* qp, const float* kp, const float* vp, const float* gp, long long ld,
+                            const void* cs_table, int rot, int pairs, float key_scale, const float* decay, float eps,
+                            float* state, long long slot_stride, const int* cu_q, const int* slots, void* out,
+                            int act_dt, int n_requests, int H, int dk, int dv, int gate_kind, const int* seg_t0,
+                            const int* seg_t1, const int* seg_req, const int* seg_flags, const int* req_item0,
+                            const int* req_items, int n_items, float* carry, cudaStream_t stream) {
+    if (n_requests <= 0) return 0;
+    if (dk <= 0 || dk > 256 || dv <= 0 || dv > 256 || H <= 0 || rot < 0 || rot > dk || (rot & 1) || (rot && !cs_table) ||
+        (gate_kind && !gp))
+        return (int)cudaErrorInvalidValue;
+    const int dkmax = ret_dkmax(dk), threads = ret_threads(dv), dvp = threads / RET_PARTS * 2;
+    TimeSegments seg = {seg_t0, seg_t1, seg_req, seg_flags, req_item0, req_items, carry, nullptr, n_items};
+    if (n_items > 0 && (!seg_t0 || !seg_t1 || !seg_req || !seg_flags || !req_item0 || !req_items || !carry))
+        return (int)cudaErrorInvalidValue;
+    const size_t smem = ((size_t)2 * RET_TOK * (2 * dkmax + 2 * dvp) + (size_t)RET_TOK * dvp) * sizeof(float);
+#define LAUNCH(TA, DKMAX, MAXT)                                                                                     \
+    return launch_retention<TA, DKMAX, MAXT>(n_requests, threads, smem, stream, qp, kp, vp, gp, ld, cs_table, rot,   \
+                                             pairs, key_scale, decay, eps, state, slot_stride, cu_q, slots, out, H,  \
+                                             dk, dv, gate_kind, seg)
+#define BY_D(TA)                                                                                               \
+    do {                                                                                                       \
+        if (threads > 512) {                                                                                   \
+            if (dkmax == 32) { LAUNCH(TA, 32, 1024); }                                                         \
+            if (dkmax == 64) { LAUNCH(TA, 64, 1024); }                                                         \
+            if (dkmax == 128) { LAUNCH(TA, 128, 1024); }                                                       \
+            LAUNCH(TA, 256, 1024);                                                                             \
+        }                                                                                                      \
+        if (dkmax == 32) { LAUNCH(TA, 32, 512); }                                                              \
+        if (dkmax == 64) { LAUNCH(TA, 64, 512); }                                                              \
+        if (dkmax == 128) { LAUNCH(TA, 128, 512); }                                                            \
+        LAUNCH(TA, 256, 512);                                                                                  \
+    } while (0)
+    if (act_dt == RLLM_F32) BY_D(float);
+    BY_D(bf16);
+#undef BY_D
+#undef LAUNCH
+}
+
+// Floats of a request's retention state for H heads of dk x dv (no device needed).
+RLLM_API long long rllm_retention_state_floats(int H, int dk, int dv) {
+    return (long long)H * ret_dkmax(dk) * (ret_threads(dv) / RET_PARTS * 2);
+}
+
 RLLM_PACKED(rllm_conv_silu)
+RLLM_PACKED(rllm_retention)
 RLLM_PACKED(rllm_selective_scan)
 RLLM_PACKED(rllm_token_shift)
 RLLM_PACKED(rllm_wkv)

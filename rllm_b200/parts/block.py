@@ -15,7 +15,8 @@ model's final norm, or a junction, for the last one).  A layer whose spec has no
 has the mixer sublayer only.  Such blocks take the plain path below (no deferred norms, no
 accumulation into the stream by the products).
 
-``post_norm`` (at the end of this file) puts the norms on the sublayers' outputs instead.
+``post_norm`` (further down) puts the norms on the sublayers' outputs instead, ``sandwich_norm`` (at the
+end of this file) on both sides of each sublayer.
 
 A block's interface: ``__init__(layer_spec, runtime)`` builds its parts from the registries;
 ``parts()`` lists them; ``forward(x, pending, ctx, cache) -> pending``.
@@ -162,3 +163,81 @@ class OutputNormBlock:
             f = self.ffn.forward(h, ctx)
             self.norm_ffn.join(x, f, copy)
         return None
+
+
+class PreparedRows:
+    """What a ``sandwich_norm`` block hands the block after it: the stream is complete and `h` holds the
+    rows of the next block's first norm already (made by the kernel that joined the last output)."""
+    __slots__ = ("h",)
+
+    def __init__(self, h):
+        self.h = h
+
+
+@register_part("block", "sandwich_norm")
+class SandwichNormBlock:
+    """A norm before AND after each sublayer:
+
+        x += norm_mixer_out(mixer(norm_mixer(x)));  x += norm_ffn_out(ffn(norm_ffn(x)))
+
+    (a spec without a feed-forward: the first only).  The stream is float32.  The kernel that joins a
+    sublayer's normed output to the stream also makes the rows of the norm that reads the stream next
+    (`Norm.join_then`): the feed-forward's first norm, and the first norm of the block that follows
+    when that block is one of this kind (`next_entry`), which then gets them as `PreparedRows`.
+    Nothing is owed to the stream when the block returns."""
+
+    CAPTURE_SAFE = True
+    TRACEABLE = False
+    DEFERS_NORM = True            # the model hands `next_entry` to blocks that say so
+
+    def __init__(self, layer_spec, runtime):
+        self.runtime = runtime
+        norms = layer_spec.norms
+        self.norm_mixer = build_part("norm", norms["mixer"], runtime)
+        self.norm_mixer_out = build_part("norm", norms["mixer_out"], runtime)
+        self.mixer = build_part("mixer", layer_spec.mixer, runtime)
+        self.ffn = build_part("ffn", layer_spec.ffn, runtime) if layer_spec.ffn is not None else None
+        self.norm_ffn = build_part("norm", norms["ffn"], runtime) if self.ffn is not None else None
+        self.norm_ffn_out = build_part("norm", norms["ffn_out"], runtime) if self.ffn is not None else None
+        self.position = (build_part("position", layer_spec.position, runtime)
+                         if layer_spec.position is not None else None)
+        self.CAPTURE_SAFE = all(getattr(p, "CAPTURE_SAFE", False) for p in self.parts())
+
+    def parts(self):
+        ps = [self.norm_mixer, self.norm_mixer_out, self.mixer]
+        if self.ffn is not None:
+            ps += [self.norm_ffn, self.norm_ffn_out, self.ffn]
+        if self.position is not None:
+            ps.append(self.position)
+        return ps
+
+    def entry(self):
+        return self.norm_mixer, self.mixer
+
+    @staticmethod
+    def _join(norm_out, x, y, norm_next):
+        """x += norm_out(y); the rows of norm_next(x) if that norm can be made in the same kernel."""
+        if norm_next is not None and hasattr(norm_out, "join_then") and hasattr(norm_next, "deferrable"):
+            return norm_out.join_then(x, y, norm_next)
+        norm_out.join(x, y)
+        return None
+
+    def forward(self, x, pending, ctx, cache, next_entry=None):
+        if isinstance(pending, PreparedRows):
+            h = pending.h
+        elif pending is not None:
+            raise ValueError("sandwich_norm: the block before still owes the stream something; "
+                             "blocks of this kind join their outputs themselves")
+        else:
+            h = self.norm_mixer.forward(x)
+        a = self.mixer.forward(h, ctx, cache, self.position)
+        nxt = next_entry[0] if next_entry is not None else None
+        if self.ffn is None:
+            h = self._join(self.norm_mixer_out, x, a, nxt)
+            return PreparedRows(h) if h is not None else None
+        h = self._join(self.norm_mixer_out, x, a, self.norm_ffn)
+        if h is None:
+            h = self.norm_ffn.forward(x)
+        f = self.ffn.forward(h, ctx)
+        h = self._join(self.norm_ffn_out, x, f, nxt)
+        return PreparedRows(h) if h is not None else None

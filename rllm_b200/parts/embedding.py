@@ -6,7 +6,8 @@ float32, W its own tensor or, when `tied_to` names one, the embedding table
 (crates/rllm-model/src/qwen3.rs:151-154, 232).
 
 Options: the embedding may be followed by an RMSNorm of its own (`norm`: the weight's name,
-`norm_eps`); the logits may be capped, logits <- softcap * tanh(logits / softcap) (`softcap`).
+`norm_eps`); the logits may be capped, logits <- softcap * tanh(logits / softcap) (`softcap`), or
+multiplied by a constant (`scale`).
 """
 from __future__ import annotations
 
@@ -59,6 +60,7 @@ class LMHead(Part):
         self.tied_to = params.get("tied_to")
         self.name = params.get("tensor") or self.prefix + "weight"
         self.softcap = float(params.get("softcap", 0.0) or 0.0)
+        self.scale = float(params.get("scale", 1.0))
         self.weight = None
 
     def expected_tensors(self):
@@ -81,4 +83,6 @@ class LMHead(Part):
         logits = ops.linear(h, self.weight, out_dtype=torch.float32)
         if self.softcap > 0.0:
             ops.softcap_rows(logits, self.softcap)
+        if self.scale != 1.0:
+            ops.axpby(self.scale, logits, 0.0, logits, logits)
         return logits

@@ -4,7 +4,8 @@ out = v * (1 / sqrt(mean(v^2) + eps)) * weight, v = x (+ delta); the weight mult
 directly (no 1 + w), statistics in float32 (AxiomOperator/rllm:
 crates/rllm-cpu/src/lib.rs:241-254; the fusion with the residual add is
 crates/rllm-cuda/kernels/kernels.cu:794-820 and crates/rllm-model/src/qwen3.rs:202-208).
-Parameters: size, eps, optionally `tensor` (the weight's full name).  Tensor: <prefix>weight
+Parameters: size, eps, optionally `tensor` (the weight's full name) and `one_plus` (the stored
+weight lies around zero and multiplies as 1 + w; the sum is formed once, in float32, at load).  Tensor: <prefix>weight
 [size], kept in float32.  `delta_scale`: the delta joins the stream multiplied by it.  `join(x, y)`: the norm of a sublayer's
 output, x += norm(y) * weight.
 """
@@ -26,13 +27,15 @@ class RMSNorm(Norm):
         self.size = int(params["size"])
         self.eps = float(params["eps"])
         self.name = params.get("tensor") or self.prefix + "weight"
+        self.one_plus = bool(params.get("one_plus", False))
         self.weight = None
 
     def expected_tensors(self):
-        return {self.name: ((self.size,), "norm")}
+        return {self.name: ((self.size,), "norm0" if self.one_plus else "norm")}
 
     def load(self, tensors):
-        self.weight = self._to_device(tensors[self.name], torch.float32)
+        w = tensors[self.name].to(torch.float32)
+        self.weight = self._to_device(1.0 + w if self.one_plus else w, torch.float32)
 
     def deferrable(self):
         """(weight, eps) for a product kernel that prepares this norm in its epilogue (the division by
@@ -44,6 +47,14 @@ class RMSNorm(Norm):
         stream `x` (in place).  `copy`, if given, also takes the new x in its own type (the operand of
         the next product).  Returns `copy`, or x."""
         return ops.norm_rows(y, self.weight, self.eps, x=x, add=True, low=copy)
+
+    def join_then(self, x, y, nxt):
+        """x += y / rms(y) * weight, and in the same kernel the rows of the norm `nxt` of the new x (in
+        the runtime's type): a norm on a sublayer's output followed by the norm in front of the next
+        sublayer."""
+        w_next, eps_next = nxt.deferrable()
+        out = torch.empty(x.shape, dtype=self.runtime.dtype, device=x.device)
+        return ops.join_norm_rows(y, self.weight, self.eps, x, w_next, eps_next, out)
 
     def forward(self, x, delta=None, rows=None, write_x=True, delta_scale=1.0):
         n = x.shape[0] if rows is None else rows.numel()

@@ -82,8 +82,10 @@ class RotaryNeox(Part):
 
 @register_part("position", "rotary_scaled")
 class RotaryScaled(Part):
-    """Rotate-half rotary encoding over the first `dims` entries of a head (the rest pass), with
-    optional YaRN-style frequency scaling.
+    """Rotary encoding over the first `dims` entries of a head (the rest pass), with optional
+    YaRN-style frequency scaling.  `layout` "half" (default): entry i turns with entry i + dims/2;
+    "pairs": entry 2i turns with entry 2i + 1.  In both, the pair (u, v) at position p becomes
+    (u cos a - v sin a, v cos a + u sin a) with a = p * f_i.
 
     f_i = base^(-2i / dims) for i < dims/2.  With `scaling` = {factor, original, fast, slow}: let
     dim(t) = dims * ln(original / (2 pi t)) / (2 ln base), lo = max(floor(dim(fast)), 0),
@@ -92,9 +94,11 @@ class RotaryScaled(Part):
     `mult` = 0.1 ln(factor) + 1.  Frequencies are worked out in double precision on the host and
     rounded once; angles (position * frequency), cos and sin are float32 on the device.
 
-    Parameters: dims, base, scaling (or None).  No tensors.  The part offers `table()` (the
-    frequencies), `mult` and `angles(ctx)` (cos, sin per token and pair, once per pass); the mixer's
-    own kernel applies them."""
+    Parameters: dims, base, scaling (or None), layout.  No tensors.  The part offers `table()` (the
+    frequencies), `mult` and `angles(ctx)` (cos, sin per token and pair, once per pass) to mixers whose
+    own kernel applies them, and `apply_and_store` to the attention part: RMS norm per head with a
+    weight, then the rotation, queries out, keys and values (heads of `v_head_dim` entries) into the
+    pages; `has_kv` False: the rows hold queries only."""
     CAPTURE_SAFE = True
 
     def __init__(self, params, prefix, runtime):
@@ -119,6 +123,9 @@ class RotaryScaled(Part):
                 ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
                 f[i] = f[i] / factor * ramp + f[i] * (1.0 - ramp)
             self.mult = 0.1 * math.log(factor) + 1.0
+        self.layout = params.get("layout") or "half"
+        if self.layout not in ("half", "pairs"):
+            raise PartError(f"rotary_scaled: layout {self.layout!r} is not known ('half', 'pairs')")
         self._key = ("rotary_scaled", self.dims, tuple(f))
         self.freq = torch.tensor(f, dtype=torch.float64).to(torch.float32).to(runtime.device)
 
@@ -133,3 +140,13 @@ class RotaryScaled(Part):
             with ops.untraced():
                 table = ctx.scratch[self._key] = ops.rope_table(ctx.positions, self.freq)
         return table
+
+    def apply_and_store(self, qkv, q_norm_w, k_norm_w, eps, ctx, cache, q_out, H, K, head_dim, v_head_dim=None,
+                        has_kv=True):
+        from ..csrc import ops
+        if self.mult != 1.0:
+            raise PartError("rotary_scaled: apply_and_store does not take scaled frequencies")
+        return ops.head_norm_rope_store(qkv, q_norm_w, k_norm_w, self.angles(ctx), min(self.dims, head_dim),
+                                        self.layout == "pairs", cache.slots, q_out, cache.k, cache.v, H, K, head_dim,
+                                        v_head_dim or head_dim, cache.block_size, eps, has_kv=has_kv,
+                                        write_kv=cache.write)

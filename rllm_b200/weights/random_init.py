@@ -25,7 +25,7 @@ def _generator(seed: int, name: str, device="cpu") -> torch.Generator:
 
 def random_tensors(expected: dict, seed: int, dtype=torch.bfloat16, std=0.02, norm_std=0.1,
                    device="cpu") -> dict:
-    """`expected`: name -> (shape, role) with role 'norm' (1 + noise), 'mix' (inside (0, 1)), 'conv'
+    """`expected`: name -> (shape, role) with role 'norm' (1 + noise), 'norm0' and 'unit' (noise of its own size), 'mix' (inside (0, 1)), 'conv'
     (noise / sqrt(taps)) or anything else (noise)."""
     out = {}
     for name, (shape, role) in expected.items():
@@ -36,6 +36,10 @@ def random_tensors(expected: dict, seed: int, dtype=torch.bfloat16, std=0.02, no
         t = torch.randn(shape, generator=g, dtype=torch.float32, device=device)
         if role == "norm":
             t = 1.0 + norm_std * t
+        elif role == "norm0":                # a norm weight stored around zero (applied as 1 + w)
+            t = norm_std * t
+        elif role == "unit":                 # numbers of the order of 1 (a sink of a softmax, a score's correction)
+            t = 0.5 * t
         elif role == "mix":                  # interpolation weights between two rows: inside (0, 1)
             t = torch.sigmoid(t)
         elif role == "conv":                 # a few taps per channel: of the order of 1 / taps
