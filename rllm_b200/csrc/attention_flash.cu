@@ -49,7 +49,14 @@ struct FlashParams {
     int chunk;                // > 0: a token sees only the keys of its own run of `chunk` positions (counted from 0)
     float cap_in, cap_out;    // capped scores (cap_out > 0): v = cap_out * tanh(s * cap_in), cap_in = scale / cap,
                               // cap_out = cap * log2(e)
+    const float* sink;        // [H] or null: exp(sink[h]) joins the denominator of head h's softmax (no key, no value,
+                              // not scaled); added once, where a row is normalized
 };
+
+// what a head's sink adds to a row's denominator whose running maximum (base 2) is m
+__device__ __forceinline__ float flash_sink_term(const FlashParams& p, int head, float m) {
+    return p.sink ? exp2f(p.sink[head] * 1.4426950408889634f - m) : 0.f;
+}
 
 // score -> exponent of the softmax (base 2).  Capped: tanh(x) = 1 - 2 / (e^(2x) + 1), which is exact in
 // both tails and has an absolute error of about 1e-7 (times the cap: far below a bfloat16 key's rounding).
@@ -321,6 +328,7 @@ __global__ void __launch_bounds__(NW * 32) paged_flash_attention_kernel(const Fl
         }
     } else {
         if (valid0) {
+            l0 += flash_sink_term(p, head0 + hl0, m0);
             const float inv = l0 > 0.f ? 1.0f / l0 : 0.f;
             bf16* po = p.out + ((size_t)(tok0 + tl0) * p.H + head0 + hl0) * HD;
 #pragma unroll
@@ -328,6 +336,7 @@ __global__ void __launch_bounds__(NW * 32) paged_flash_attention_kernel(const Fl
                 *reinterpret_cast<uint32_t*>(po + 8 * j + 2 * t) = pack_bf16(o[j][0] * inv, o[j][1] * inv);
         }
         if (valid1) {
+            l1 += flash_sink_term(p, head0 + hl1, m1);
             const float inv = l1 > 0.f ? 1.0f / l1 : 0.f;
             bf16* po = p.out + ((size_t)(tok0 + tl1) * p.H + head0 + hl1) * HD;
 #pragma unroll
@@ -633,6 +642,7 @@ __global__ void __launch_bounds__(32) paged_decode_attention_kernel(const FlashP
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
             if (!validc[x]) continue;
+            lsum[x] += flash_sink_term(p, head0 + hlc[x], mx[x]);
             const float inv = lsum[x] > 0.f ? 1.0f / lsum[x] : 0.f;
             bf16* po = p.out + ((size_t)(tok0 + tlc[x]) * p.H + head0 + hlc[x]) * HD;
 #pragma unroll
@@ -701,6 +711,7 @@ __global__ void __launch_bounds__(HD) paged_flash_combine_kernel(const FlashPara
         const float w = wgt[z];
         if (w > 0.f) { num += po[z * zstride] * w; den += wgt[n_splits + z] * w; }
     }
+    if (den > 0.f) den += flash_sink_term(p, head0 + hl, M);
     p.out[((size_t)(tok0 + tl) * p.H + head0 + hl) * HD + d] = from_f<bf16>(den > 0.f ? num / den : 0.f);
 }
 
@@ -745,13 +756,15 @@ static int launch_flash(const FlashParams& p, int mode, int n_tiles, int n_split
 // the LAST of the n_splits splits then belongs to them, so the caller counts one split more.
 // chunk > 0: the chunked mask (runs of `chunk` positions counted from 0; a token sees the keys of its
 // own run up to itself).  softcap > 0: scores go through softcap * tanh(s * scale / softcap).
-RLLM_API int rllm_paged_flash_attention_masked(const void* q, const void* k_cache, const void* v_cache, void* out,
-                                               float* part_o, float* part_ml, const int* positions, const int* cu_q,
-                                               const int* block_table, int table_stride, const int* tile_req,
-                                               const int* tile_tok0, int n_tiles, int H, int K, int hd, int bs,
-                                               float scale, int window, int keep_first, int mode, int TT, int GH,
-                                               int head_chunks, int split_keys, int n_splits, long long n_pages,
-                                               int* err, int chunk, float softcap, cudaStream_t stream) {
+// sink (one float per query head, or null): exp(sink[h]) joins the softmax's denominator of head h.
+RLLM_API int rllm_paged_flash_attention_sink(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                             float* part_o, float* part_ml, const int* positions, const int* cu_q,
+                                             const int* block_table, int table_stride, const int* tile_req,
+                                             const int* tile_tok0, int n_tiles, int H, int K, int hd, int bs,
+                                             float scale, int window, int keep_first, int mode, int TT, int GH,
+                                             int head_chunks, int split_keys, int n_splits, long long n_pages,
+                                             int* err, int chunk, float softcap, const float* sink,
+                                             cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (chunk < 0 || softcap < 0.f) return (int)cudaErrorInvalidValue;
     if (keep_first < 0 || (keep_first > 0 && mode == 1 && n_splits < 2)) return (int)cudaErrorInvalidValue;
@@ -772,9 +785,23 @@ RLLM_API int rllm_paged_flash_attention_masked(const void* q, const void* k_cach
     p.chunk = chunk;
     p.cap_in = softcap > 0.f ? scale / softcap : 0.f;
     p.cap_out = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
+    p.sink = sink;
     if (hd == 128) return launch_flash<128>(p, mode, n_tiles, n_splits, stream);
     if (hd == 64) return launch_flash<64>(p, mode, n_tiles, n_splits, stream);
     return (int)cudaErrorInvalidValue;
+}
+
+RLLM_API int rllm_paged_flash_attention_masked(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                               float* part_o, float* part_ml, const int* positions, const int* cu_q,
+                                               const int* block_table, int table_stride, const int* tile_req,
+                                               const int* tile_tok0, int n_tiles, int H, int K, int hd, int bs,
+                                               float scale, int window, int keep_first, int mode, int TT, int GH,
+                                               int head_chunks, int split_keys, int n_splits, long long n_pages,
+                                               int* err, int chunk, float softcap, cudaStream_t stream) {
+    return rllm_paged_flash_attention_sink(q, k_cache, v_cache, out, part_o, part_ml, positions, cu_q, block_table,
+                                           table_stride, tile_req, tile_tok0, n_tiles, H, K, hd, bs, scale, window,
+                                           keep_first, mode, TT, GH, head_chunks, split_keys, n_splits, n_pages, err,
+                                           chunk, softcap, nullptr, stream);
 }
 
 RLLM_API int rllm_paged_flash_attention_kept(const void* q, const void* k_cache, const void* v_cache, void* out,
@@ -861,3 +888,4 @@ RLLM_API int rllm_paged_flash_decode_static(const void* q, const void* k_cache, 
 RLLM_PACKED(rllm_paged_flash_attention)
 RLLM_PACKED(rllm_paged_flash_attention_kept)
 RLLM_PACKED(rllm_paged_flash_attention_masked)
+RLLM_PACKED(rllm_paged_flash_attention_sink)

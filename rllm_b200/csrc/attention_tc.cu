@@ -71,6 +71,8 @@ struct AttnTcParams {
     int chunk;                  // > 0: a token sees only the keys of its own run of `chunk` positions (counted from 0)
     float cap_in, cap_pre;      // capped scores (cap_pre > 0): s <- cap_pre * tanh(s * cap_in) before the scale, with
                                 // cap_in = scale / cap and cap_pre = cap / scale
+    const float* sink;          // [H] or null: exp(sink[h]) joins the denominator of head h's softmax (no key, no value,
+                                // not scaled); added once, where a row is normalized
 };
 
 // K-major, 128-byte swizzle (Q, K, P): see smem_desc_sw128.  MN-major (V: dims contiguous):
@@ -453,6 +455,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             const float m_other = mg_sh[r];
             if (n_kt > 1 && m_other != -INFINITY) l = (m_mine == -INFINITY ? 0.f : l * exp2f(m_mine - m_fin)) + l_sh[r] * exp2f(m_other - m_fin);
             else if (m_mine != -INFINITY && m_mine != m_fin) l *= exp2f(m_mine - m_fin);
+            if (p.sink && l > 0.f) l += exp2f(p.sink[head0 + hl] * 1.4426950408889634f - m_fin);
         }
         pdl_launch_dependents();
         if (wg == 0 && __all_sync(0xffffffffu, ok)) {              // warp-uniform: the TMEM loads are warp-wide
@@ -488,11 +491,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 // q, out [n, H, 128] bfloat16; caches [pages, K, bs, 128] bfloat16; tiles of TT = 128 / (H / K) tokens.
 // Returns cudaErrorInvalidValue for shapes outside the limits named at the top of this file.
 // chunk > 0: the chunked mask; softcap > 0: scores go through softcap * tanh(s * scale / softcap).
-RLLM_API int rllm_attention_tc_masked(const void* q, const void* k_cache, const void* v_cache, void* out, int n_tokens,
-                                      long long n_pages, const int* positions, const int* cu_q, const int* block_table,
-                                      int table_stride, const int* tile_req, const int* tile_tok0, int n_tiles, int H,
-                                      int K, int hd, int bs, float scale, int window, int chunk, float softcap, int* err,
-                                      cudaStream_t stream) {
+// sink (one float per query head, or null): exp(sink[h]) joins the softmax's denominator of head h.
+RLLM_API int rllm_attention_tc_sink(const void* q, const void* k_cache, const void* v_cache, void* out, int n_tokens,
+                                    long long n_pages, const int* positions, const int* cu_q, const int* block_table,
+                                    int table_stride, const int* tile_req, const int* tile_tok0, int n_tiles, int H,
+                                    int K, int hd, int bs, float scale, int window, int chunk, float softcap,
+                                    const float* sink, int* err, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (chunk < 0 || softcap < 0.f || !(scale > 0.f)) return (int)cudaErrorInvalidValue;
     if (hd != AT_HD || K <= 0 || H % K || bs < 8 || bs > 128 || (bs & (bs - 1)) || !err) return (int)cudaErrorInvalidValue;
@@ -526,6 +530,7 @@ RLLM_API int rllm_attention_tc_masked(const void* q, const void* k_cache, const 
     p.chunk = chunk;
     p.cap_in = softcap > 0.f ? scale / softcap : 0.f;
     p.cap_pre = softcap > 0.f ? softcap / scale : 0.f;
+    p.sink = sink;
     constexpr int smem = (1 + AT_KS + AT_VS) * AT_TILE_BYTES + 1024;
     static bool attr_set = false;
     if (!attr_set) {
@@ -534,6 +539,16 @@ RLLM_API int rllm_attention_tc_masked(const void* q, const void* k_cache, const 
         attr_set = true;
     }
     return rllm_launch(attention_tc_kernel, dim3(n_tiles, K), dim3(AT_THREADS), smem, stream, tq, tk, tv, p);
+}
+
+RLLM_API int rllm_attention_tc_masked(const void* q, const void* k_cache, const void* v_cache, void* out, int n_tokens,
+                                      long long n_pages, const int* positions, const int* cu_q, const int* block_table,
+                                      int table_stride, const int* tile_req, const int* tile_tok0, int n_tiles, int H,
+                                      int K, int hd, int bs, float scale, int window, int chunk, float softcap, int* err,
+                                      cudaStream_t stream) {
+    return rllm_attention_tc_sink(q, k_cache, v_cache, out, n_tokens, n_pages, positions, cu_q, block_table, table_stride,
+                                  tile_req, tile_tok0, n_tiles, H, K, hd, bs, scale, window, chunk, softcap, nullptr, err,
+                                  stream);
 }
 
 RLLM_API int rllm_attention_tc(const void* q, const void* k_cache, const void* v_cache, void* out, int n_tokens,
@@ -550,3 +565,4 @@ TC_DEFINE_WAIT_CONTROLS(rllm_attn_tc)
 // the packed-argument forms (common.cuh) for the host runtime's replay of recorded launches
 RLLM_PACKED(rllm_attention_tc)
 RLLM_PACKED(rllm_attention_tc_masked)
+RLLM_PACKED(rllm_attention_tc_sink)

@@ -1566,15 +1566,17 @@ class AttentionPlan:
 
 def paged_flash_attention(q, k_cache, v_cache, out, positions, cu_q, block_table, tile_req, tile_tok0,
                           n_tiles, H, K, hd, block_size, scale, window, mode, TT, GH, head_chunks,
-                          split_keys=DECODE_SPLIT_KEYS, n_splits=1, keep_first=0, chunk=0, softcap=0.0):
+                          split_keys=DECODE_SPLIT_KEYS, n_splits=1, keep_first=0, chunk=0, softcap=0.0, sink=None):
     """Tensor-core paged attention; mode 0: prefill shape, mode 1: decode shape with split keys
     (allocates the partials as scratch).  keep_first (with a window): the first keys of a request stay
     visible; in mode 1 one split more, the last, is theirs.  chunk: the chunked mask (runs of that many
-    positions); softcap: capped scores.  See attention_flash.cu."""
+    positions); softcap: capped scores; sink (float32 [H]): exp(sink[h]) joins the denominator of head
+    h's softmax.  See attention_flash.cu."""
     if keep_first and window and mode == 1:
         n_splits += 1
-    _need_cuda(q, k_cache, v_cache, out, positions, cu_q, block_table, tile_req, tile_tok0)
+    _need_cuda(q, k_cache, v_cache, out, positions, cu_q, block_table, tile_req, tile_tok0, sink)
     _need_contig(q=q, k_cache=k_cache, v_cache=v_cache, out=out)
+    assert sink is None or (sink.dtype == torch.float32 and sink.numel() == H and sink.is_contiguous())
     if q.dtype != torch.bfloat16 or hd not in FLASH_HEAD_DIMS:
         raise KernelError(f"paged_flash_attention takes bfloat16 and a head size of 64 or 128, got {q.dtype}, {hd}")
     assert block_table.stride(1) == 1
@@ -1583,13 +1585,13 @@ def paged_flash_attention(q, k_cache, v_cache, out, positions, cu_q, block_table
         rows = n_tiles * K * head_chunks * n_splits * TT * GH
         part_o = torch.empty(rows * hd, dtype=torch.float32, device=q.device)
         part_ml = torch.empty(rows * 2, dtype=torch.float32, device=q.device)
-    _check(_lib("attn").rllm_paged_flash_attention_masked(
+    _check(_lib("attn").rllm_paged_flash_attention_sink(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(positions),
         _ptr(cu_q), _ptr(block_table), c_int(block_table.stride(0)), _ptr(tile_req), _ptr(tile_tok0),
         c_int(n_tiles), c_int(H), c_int(K), c_int(hd), c_int(block_size), c_float(scale), c_int(window),
         c_int(keep_first if window else 0), c_int(mode), c_int(TT), c_int(GH), c_int(head_chunks), c_int(split_keys),
         c_int(n_splits), c_longlong(k_cache.shape[0]), _ptr(error_word(q.device)), c_int(chunk), c_float(softcap),
-        _stream()),
+        _ptr(sink), _stream()),
         "paged_flash_attention")
     global _launches
     if mode == 1:
@@ -1604,18 +1606,19 @@ def attention_tc_ok(q, hd, block_size, H, K) -> bool:
 
 
 def attention_tc(q, k_cache, v_cache, out, positions, cu_q, block_table, tile_req, tile_tok0, n_tiles, H, K, hd,
-                 block_size, scale, window, chunk=0, softcap=0.0):
+                 block_size, scale, window, chunk=0, softcap=0.0, sink=None):
     """Prefill attention on the tcgen05 tensor cores (S and O in tensor memory); see attention_tc.cu."""
-    _need_cuda(q, k_cache, v_cache, out, positions, cu_q, block_table, tile_req, tile_tok0)
+    _need_cuda(q, k_cache, v_cache, out, positions, cu_q, block_table, tile_req, tile_tok0, sink)
+    assert sink is None or (sink.dtype == torch.float32 and sink.numel() == H and sink.is_contiguous())
     _need_contig(q=q, k_cache=k_cache, v_cache=v_cache, out=out)
     if not attention_tc_ok(q, hd, block_size, H, K):
         raise KernelError("attention_tc takes bfloat16, head size 128, a power-of-two page size from 8 to 128 and "
                           "a number of query heads per key/value head that divides 128")
-    st = _lib("attn_tc").rllm_attention_tc_masked(
+    st = _lib("attn_tc").rllm_attention_tc_sink(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), c_int(q.shape[0]), c_longlong(k_cache.shape[0]),
         _ptr(positions), _ptr(cu_q), _ptr(block_table), c_int(block_table.stride(0)), _ptr(tile_req),
         _ptr(tile_tok0), c_int(n_tiles), c_int(H), c_int(K), c_int(hd), c_int(block_size), c_float(scale),
-        c_int(window), c_int(chunk), c_float(softcap), _ptr(error_word(q.device)), _stream())
+        c_int(window), c_int(chunk), c_float(softcap), _ptr(sink), _ptr(error_word(q.device)), _stream())
     if st >= 30000:
         raise KernelError(f"attention_tc: tensor map encoding failed (CUresult {st - 30000})")
     _check(st, "attention_tc")
@@ -1748,7 +1751,7 @@ def paged_attention(q, k_cache, v_cache, out, ctx, block_table, H, K, hd, block_
     windows that keep the first keys take the mma.sync kernels, not the tcgen05 one."""
     hdv = hd if not v_head_dim else int(v_head_dim)
     keep_first = keep_first if window else 0
-    if q.dtype != torch.bfloat16 or hd not in FLASH_HEAD_DIMS or hdv != hd or sink is not None:
+    if q.dtype != torch.bfloat16 or hd not in FLASH_HEAD_DIMS or hdv != hd:
         return paged_attention_generic(q, k_cache, v_cache, out, ctx.positions, ctx.seq_ids, block_table,
                                        H, K, hd, block_size, scale, window, keep_first, hdv, chunk, softcap, sink)
     key = (H // K, window, chunk)
@@ -1757,14 +1760,14 @@ def paged_attention(q, k_cache, v_cache, out, ctx, block_table, H, K, hd, block_
         plan = ctx.plans[key] = AttentionPlan(ctx, H, K, window, q.device, chunk)
     if plan.n_pre and plan.n_tc and USE_ATTENTION_TC and attention_tc_ok(q, hd, block_size, H, K) and not keep_first:
         attention_tc(q, k_cache, v_cache, out, ctx.positions, ctx.cu_q, block_table, plan.t_req, plan.t_tok,
-                     plan.n_tc, H, K, hd, block_size, scale, window, chunk, softcap)
+                     plan.n_tc, H, K, hd, block_size, scale, window, chunk, softcap, sink)
     elif plan.n_pre:
         paged_flash_attention(q, k_cache, v_cache, out, ctx.positions, ctx.cu_q, block_table, plan.p_req,
                               plan.p_tok, plan.n_pre, H, K, hd, block_size, scale, window, 0, plan.TTp,
-                              plan.GHp, plan.chunks_p, keep_first=keep_first, chunk=chunk, softcap=softcap)
+                              plan.GHp, plan.chunks_p, keep_first=keep_first, chunk=chunk, softcap=softcap, sink=sink)
     if plan.n_dec:
         paged_flash_attention(q, k_cache, v_cache, out, ctx.positions, ctx.cu_q, block_table, plan.d_req,
                               plan.d_tok, plan.n_dec, H, K, hd, block_size, scale, window, 1, plan.TTd,
                               plan.GHd, plan.chunks_d, DECODE_SPLIT_KEYS, plan.n_splits, keep_first=keep_first,
-                              chunk=chunk, softcap=softcap)
+                              chunk=chunk, softcap=softcap, sink=sink)
     return out
