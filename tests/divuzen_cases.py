@@ -155,9 +155,19 @@ def make_weights(cfg, seed, dtype=torch.float32, gain=1.3):
     return out
 
 
-def oracle(cfg, weights, tokens, streams=None):
-    """float64 logits [T, vocab] of the plain implementation from the weights as stored."""
-    return plain_divuzen.forward(cfg, weights, tokens, streams)
+def oracle(cfg, weights, tokens, streams=None, given=None, slack=0.0):
+    """float64 logits [T, vocab] of the plain implementation from the weights as stored.  The result
+    carries `margin` [T], how far each token's choice of experts is from another choice (the smallest
+    over the layers of routed experts, infinite without any), and `again(given, slack)`: the logits once
+    more with somebody else's choices taken over where they are as good as the plain router's own."""
+    margins = []
+    logits = plain_divuzen.forward(cfg, weights, tokens, streams, margins=margins, given=given, slack=slack)
+    m = torch.full((len(tokens),), math.inf, dtype=torch.float64)
+    for per_token in margins:
+        m = torch.minimum(m, torch.tensor(per_token, dtype=torch.float64))
+    logits.margin = m
+    logits.again = lambda given, slack: oracle(cfg, weights, tokens, given=given, slack=slack)
+    return logits
 
 
 def sharpened(cfg, factor, layers=None):
@@ -195,7 +205,11 @@ def marked_attention(cfg, w, asker, target):
     return w
 
 
-def build_engine(cfg, weights, dtype, max_tokens, block_size=8, max_requests=4, use_graphs=True, device="cuda:0"):
+def build_engine(cfg, weights, dtype, max_tokens, block_size=8, max_requests=4, use_graphs=None, device="cuda:0"):
+    """`use_graphs` None: replay from graphs in float32 only (a replayed step does not show which experts
+    it chose, and in bfloat16 the comparison wants to know: see `oracle`)."""
+    if use_graphs is None:
+        use_graphs = dtype == "float32"
     from rllm_b200.config import config_from_dict
     from rllm_b200.engine import Engine
     from rllm_b200.models.model import DecoderModel, parse_dtype

@@ -112,27 +112,49 @@ def expert(h, W, p):
     return (g * torch.sigmoid(g) * (h @ W[p + "up"].T)) @ W[p + "down"].T
 
 
-def route(h_t, W, p, r):
-    """One token: (chosen experts, their weights)."""
-    E = r["experts"]
+def choose(c, r):
+    """The experts with the largest choice scores c inside the best groups (best first)."""
     groups = r.get("groups") or {"count": 1, "keep": 1}
-    s = torch.sigmoid(W[p + "router"] @ h_t)
-    c = s + W[p + "correction"]
-    per = E // groups["count"]
+    per = r["experts"] // groups["count"]
     by_group = c.view(groups["count"], per)
     score = by_group.sort(-1, descending=True).values[:, :2].sum(-1)
     kept = score.sort(descending=True, stable=True).indices[: groups["keep"]]
     masked = torch.full_like(by_group, -math.inf)
     masked[kept] = by_group[kept]
-    chosen = masked.view(-1).sort(descending=True, stable=True).indices[: r["top"]]
+    order = masked.view(-1).sort(descending=True, stable=True)
+    gaps = [math.inf]
+    if r["top"] < groups["keep"] * per:
+        gaps.append(float(order.values[r["top"] - 1] - order.values[r["top"]]))
+    if groups["keep"] < groups["count"]:
+        ranked = score.sort(descending=True).values
+        gaps.append(float(ranked[groups["keep"] - 1] - ranked[groups["keep"]]))
+    return order.indices[: r["top"]].tolist(), min(gaps)
+
+
+def route(h_t, W, p, r, margin=None, given=None, slack=0.0):
+    """One token: (chosen experts, their weights).  `margin`, a list, receives how far the choice is
+    from another one: the gap between the last chosen and the first unchosen choice score, or between
+    the last kept and the first dropped group's score, whichever is smaller.  `given`: experts that
+    somebody else chose for this token; they are taken instead if they are what this router chooses
+    once every choice score has moved by at most `slack` (theirs up, the others' down)."""
+    s = torch.sigmoid(W[p + "router"] @ h_t)
+    c = s + W[p + "correction"]
+    chosen, gap = choose(c, r)
+    if margin is not None:
+        margin.append(gap)
+    if given is not None and set(given) != set(chosen) and len(set(given)) == r["top"]:
+        lift = torch.full_like(c, -slack)
+        lift[list(given)] = slack
+        if set(choose(c + lift, r)[0]) == set(given):
+            chosen = list(given)
     w = s[chosen]
-    return chosen.tolist(), w / (w.sum() + 1e-20) * r["scale"]
+    return chosen, w / (w.sum() + 1e-20) * r["scale"]
 
 
-def moe_ff(h, W, p, mlp):
+def moe_ff(h, W, p, mlp, margins=None, given=None, slack=0.0):
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
-        chosen, w = route(h[t], W, p, mlp["router"])
+        chosen, w = route(h[t], W, p, mlp["router"], margins, (given or {}).get(t), slack)
         for j, e in enumerate(chosen):
             out[t] += w[j] * expert(h[t: t + 1], W, f"{p}e{e}.")[0]
     if mlp.get("shared"):
@@ -140,9 +162,11 @@ def moe_ff(h, W, p, mlp):
     return out
 
 
-def forward(cfg, W, tokens, streams=None, mixers=None):
+def forward(cfg, W, tokens, streams=None, mixers=None, margins=None, given=None, slack=0.0):
     """Logits [T, vocab] of one whole sequence.  `streams`, a list, receives the residual stream after
-    every layer; `mixers` each mixer's output before its norm."""
+    every layer; `mixers` each mixer's output before its norm; `margins` one list per layer of routed
+    experts with every token's distance from another choice of experts; `given` {layer: {position:
+    experts}} and `slack`: choices to take over where they are as good as this router's own (see `route`)."""
     W = {k: v.to(F64) for k, v in W.items()}
     eps = cfg["norm"]["eps"]
     x = W["embed"][torch.as_tensor(tokens, dtype=torch.long)]
@@ -162,7 +186,13 @@ def forward(cfg, W, tokens, streams=None, mixers=None):
         mlp = layer.get("mlp")
         if mlp is not None:
             h = norm_one_plus(x, W[p + "norm2"], eps)
-            f = dense_ff(h, W, p + "mlp.", mlp["limit"]) if mlp["kind"] == "dense" else moe_ff(h, W, p + "mlp.", mlp)
+            if mlp["kind"] == "dense":
+                f = dense_ff(h, W, p + "mlp.", mlp["limit"])
+            else:
+                per_token = [] if margins is not None else None
+                f = moe_ff(h, W, p + "mlp.", mlp, per_token, (given or {}).get(i), slack)
+                if margins is not None:
+                    margins.append(per_token)
             x = x + norm_one_plus(f, W[p + "norm2b"], eps)
         if streams is not None:
             streams.append(x.clone())
