@@ -147,6 +147,34 @@ def govopel_shape(width: int) -> dict:
             "norm": {"eps": 1e-6}, "logit_softcap": 30.0}
 
 
+def divuzen_shape(width: int) -> dict:
+    """A Divuzen configuration with layer sizes of a real model of that width: retention (width/256
+    heads with keys of 128 and values of 256, all of a key rotated; dense feed-forward of 3 widths),
+    attention (width/128 heads of 128, a quarter as many key/value heads, half of each head rotated,
+    sinks; 16 routed experts of 3/8 width of which a token uses 4, in 4 groups of which 2 are kept,
+    and a shared expert of 3/4 width), retention with routed experts, attention on the second layer's
+    keys and values with a dense feed-forward; that order twice: eight layer runs."""
+    heads = max(8, width // 128)
+    rh = max(4, width // 256)
+    dense = {"kind": "dense", "ff": 3 * width, "limit": 7.0}
+    moe = {"kind": "moe", "expert": {"ff": 3 * width // 8}, "shared": {"ff": 3 * width // 4},
+           "router": {"experts": 16, "top": 4, "scale": 2.5, "groups": {"count": 4, "keep": 2}}}
+    ret = {"heads": rh, "dim": 128, "vdim": 256, "rot": {"dims": 128, "base": 1000000.0},
+           "decay": [1.0 - 2.0 ** (-5.0 - 5.0 * i / max(1, rh - 1)) for i in range(rh)]}
+    att = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "rot": {"dims": 64, "base": 10000.0},
+           "scale": 128 ** -0.5}
+    layers = []
+    for base in (0, 4):
+        layers += [{"type": "retention", "mixer": ret, "mlp": dense}, {"type": "attention", "mixer": att, "mlp": moe},
+                   {"type": "retention", "mixer": ret, "mlp": moe},
+                   {"type": "attention", "mixer": dict(att, kv_from=base + 1), "mlp": dense}]
+    return {"architecture": "Divuzen", "vocab": 32768, "width": width, "layers": layers, "norm": {"eps": 1e-6},
+            "logit_scale": 0.5}
+
+
+FAMILY_SHAPES = {"falalix": falalix_shape, "govopel": govopel_shape, "divuzen": divuzen_shape}
+
+
 def falalix_compare(a):
     """Prefill (one step of 2,048 tokens) and decode (batch 8 behind 2,048-token prompts, replayed
     from CUDA graphs) of Falalix-shaped models beside Qwen3-shaped models of the same width, number
@@ -172,7 +200,7 @@ def falalix_compare(a):
         width = widths[size]
         row = {}
         for name in (family, "qwen3"):
-            fal = falalix_shape(width) if family == "falalix" else govopel_shape(width)
+            fal = FAMILY_SHAPES[family](width)
             runs = len(fal["layers"])
             if fal.get("loop"):
                 runs += (fal["loop"]["stop"] - fal["loop"]["start"]) * (fal["loop"]["times"] - 1)
@@ -255,13 +283,13 @@ def main():
     ap.add_argument("--ctx", type=int, default=None, help="tokens a request may hold (default: twice the prompt)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 / 64 and prefill")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "falalix", "govopel"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "falalix", "govopel", "divuzen"],
                     help="decode: the default line.  serving: --requests prompts of 16..2,048 tokens with 128..512 "
                          "generated tokens each through LLM.generate (continuous batching), one line of its own.  "
                          "falalix: prefill and decode of Falalix-shaped models (--sizes) beside Qwen3-shaped models of "
                          "equal width, depth and feed-forward, one line of its own.  govopel: the same for "
-                         "Govopel-shaped models")
-    ap.add_argument("--sizes", default="1k,2k,4k", help="falalix, govopel: model widths to run (1k, 2k, 4k)")
+                         "Govopel-shaped and for Divuzen-shaped models")
+    ap.add_argument("--sizes", default="1k,2k,4k", help="falalix, govopel, divuzen: model widths to run (1k, 2k, 4k)")
     ap.add_argument("--requests", type=int, default=64)
     ap.add_argument("--parallel", type=int, default=32, help="serving: requests running at once")
     ap.add_argument("--prefill-chunk", type=int, default=512, help="serving: prompt tokens per step")
@@ -275,7 +303,7 @@ def main():
         print(f"bench.py: this engine runs on one GPU; --gpus {a.gpus} is not supported")
         return 2
     a.warmup = max(a.warmup, 3)
-    if a.workload in ("falalix", "govopel"):
+    if a.workload in FAMILY_SHAPES:
         return falalix_compare(a)
     PROMPT = a.prompt_len
     CTX = a.ctx if a.ctx is not None else 2 * PROMPT

@@ -853,7 +853,7 @@ retention_kernel(const float* qp, const float* kp, const float* vp, const float*
 
 // Between the passes: a request's segments in order, S_end = c^len * S_start + local end state, in place.
 template <int DKMAX>
-__global__ void retention_combine_kernel(const float* state, long long slot_stride, const int* __restrict__ slots,
+__global__ void __launch_bounds__(1024) retention_combine_kernel(const float* state, long long slot_stride, const int* __restrict__ slots,
                                          const float* __restrict__ decay, int H, const TimeSegments seg) {
     constexpr int IPT = DKMAX / RET_PARTS;
     pdl_wait();

@@ -66,6 +66,7 @@ CASES = {
     "moe_one_each": config([att(2, 1, 12, 12, 6, mlp=moe(10, 5, 1, scale=0.6, shared=14))], width=22, vocab=43),
     "moe_groups_of_one": config([ret(1, 12, 20, 2, [0.75], mlp=moe(6, 6, 2, count=6, keep=3, shared=8))], width=18,
                                 vocab=41, logit_scale=0.25),
+    "retention_256_values": config([ret(1, 128, 256, 32, [0.9921875], mlp=dense(20))], width=24, vocab=37),
     # another layer's keys and values
     "shared_keys": config([att(4, 2, 12, 20, 4, mlp=dense(30)), ret(2, 8, 16, 8, [0.9, 0.99]),
                            att(4, 2, 12, 20, 4, scale=0.4, kv_from=0, mlp=moe(8, 8, 2, count=2, keep=1, shared=12))],

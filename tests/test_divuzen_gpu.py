@@ -563,6 +563,18 @@ def test_long_portions(dtype):
     compare(run(eng, steps), refs, dtype, "long portions")
 
 
+def test_long_portion_through_the_largest_retention_heads():
+    """Value heads of 256 entries under keys of 128 (the retention kernel's largest blocks) in a portion
+    long enough to be cut along time, then single tokens."""
+    cfg = CASES["retention_256_values"]
+    w = dc.make_weights(cfg, 14)
+    toks = dc.tokens_for(cfg, 610, 62)
+    ref = {"a": dc.oracle(cfg, w, toks)}
+    eng = dc.build_engine(cfg, w, "float32", max_tokens=640, block_size=32, max_requests=1)
+    steps = [([("a", toks[:600], [0, 127, 128, 300, 599])], [])] + one_by_one("a", toks, 600)
+    compare(run(eng, steps), ref, "float32", "largest retention heads")
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_decoding_through_graph_replay(dtype):
     """200 single-token steps of three requests behind short prompts (graphs captured per context
