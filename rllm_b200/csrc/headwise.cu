@@ -511,6 +511,86 @@ join_norm_rows_kernel(const TY* y, long long ld_y, const float* __restrict__ w_o
     for (int i = threadIdx.x; i < d; i += blockDim.x) out[t * d + i] = from_f<TO>(row[i] * r2 * w_next[i]);
 }
 
+__device__ __forceinline__ void store4(float* o, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(o) = make_float4(a, b, c, d);
+}
+__device__ __forceinline__ void store4(bf16* o, float a, float b, float c, float d) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 u;
+    u.x = *reinterpret_cast<const uint32_t*>(&lo);
+    u.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(o) = u;
+}
+
+// The same with rows in registers: float32 y, d a multiple of 4 up to NV * 4 * 256, rows 16-byte aligned.
+// A thread holds NV float4 of the row; all its loads are in flight at once.
+template <typename TO, int NV>
+__global__ void __launch_bounds__(256)
+join_norm_rows_vec_kernel(const float* y, long long ld_y, const float* __restrict__ w_out, float eps_out, float* x,
+                          const float* __restrict__ w_next, float eps_next, TO* out, int d) {
+    __shared__ float red[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t t = blockIdx.x;
+    const int d4 = d >> 2;
+    const float4* y4 = reinterpret_cast<const float4*>(y + t * ld_y);
+    float4* x4 = reinterpret_cast<float4*>(x + t * d);
+    const float4* wo4 = reinterpret_cast<const float4*>(w_out);
+    const float4* wn4 = reinterpret_cast<const float4*>(w_next);
+    float4 yv[NV], xv[NV];
+    float ss = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+        const int i = v * 256 + threadIdx.x;
+        yv[v] = i < d4 ? y4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        xv[v] = i < d4 ? x4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int v = 0; v < NV; ++v) ss += yv[v].x * yv[v].x + yv[v].y * yv[v].y + yv[v].z * yv[v].z + yv[v].w * yv[v].w;
+    ss = block_sum(ss, red);
+    const float rs = 1.0f / sqrtf(ss / (float)d + eps_out);
+    float s2 = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+        const int i = v * 256 + threadIdx.x;
+        if (i < d4) {
+            const float4 w = wo4[i];
+            xv[v].x += yv[v].x * rs * w.x;
+            xv[v].y += yv[v].y * rs * w.y;
+            xv[v].z += yv[v].z * rs * w.z;
+            xv[v].w += yv[v].w * rs * w.w;
+            x4[i] = xv[v];
+            s2 += xv[v].x * xv[v].x + xv[v].y * xv[v].y + xv[v].z * xv[v].z + xv[v].w * xv[v].w;
+        }
+    }
+    s2 = block_sum(s2, red);
+    const float r2 = 1.0f / sqrtf(s2 / (float)d + eps_next);
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+        const int i = v * 256 + threadIdx.x;
+        if (i < d4) {
+            const float4 w = wn4[i];
+            store4(out + t * d + (size_t)i * 4, xv[v].x * r2 * w.x, xv[v].y * r2 * w.y, xv[v].z * r2 * w.z,
+                   xv[v].w * r2 * w.w);
+        }
+    }
+}
+
+template <typename TO>
+static int launch_join_norm_vec(int n, int d, cudaStream_t stream, const float* y, long long ld_y, const float* w_out,
+                                float eps_out, float* x, const float* w_next, float eps_next, TO* out) {
+#define JV(NV)                                                                                                     \
+    return rllm_launch(join_norm_rows_vec_kernel<TO, NV>, dim3(n), dim3(256), 0, stream, y, ld_y, w_out, eps_out, x, \
+                       w_next, eps_next, out, d)
+    const int nv = (d / 4 + 255) / 256;
+    if (nv <= 1) { JV(1); }
+    if (nv <= 2) { JV(2); }
+    if (nv <= 4) { JV(4); }
+    if (nv <= 8) { JV(8); }
+    JV(12);
+#undef JV
+}
+
 RLLM_API int rllm_join_norm_rows(const void* y, int y_dt, long long ld_y, const float* w_out, float eps_out, float* x,
                                  const float* w_next, float eps_next, void* out, int out_dt, int n, int d,
                                  cudaStream_t stream) {
@@ -518,6 +598,14 @@ RLLM_API int rllm_join_norm_rows(const void* y, int y_dt, long long ld_y, const 
     if (d <= 0 || ld_y < d || !w_out || !w_next || !x || !out) return (int)cudaErrorInvalidValue;
     const size_t smem = (size_t)d * sizeof(float);
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
+    const auto al16 = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+    if (y_dt == RLLM_F32 && d >= 256 && (d & 3) == 0 && (ld_y & 3) == 0 && al16(y) && al16(x) && al16(w_out) && al16(w_next) &&
+        al16(out)) {
+        if (out_dt == RLLM_F32)
+            return launch_join_norm_vec<float>(n, d, stream, (const float*)y, ld_y, w_out, eps_out, x, w_next, eps_next, (float*)out);
+        if (out_dt == RLLM_BF16)
+            return launch_join_norm_vec<bf16>(n, d, stream, (const float*)y, ld_y, w_out, eps_out, x, w_next, eps_next, (bf16*)out);
+    }
     const dim3 block(d >= 2048 ? 256 : 128);
 #define LAUNCH(TY, TO)                                                                                          \
     return rllm_launch(join_norm_rows_kernel<TY, TO>, dim3(n), block, smem, stream, (const TY*)y, ld_y, w_out,   \

@@ -9,7 +9,8 @@
 //                    (ties: the lower index); weights = the winners' scores (without the correction),
 //                    divided by their sum + weight_eps when `normalize`, times route_scale.
 //   moe_pairs_gate_up  act[pair, f] = glu(Wg[e] . h[t], Wu[e] . h[t]) for every (token, chosen expert) pair:
-//                    a block per (pair, tile of columns), a warp per column, the token's row in shared memory.
+//                    a block per (pair, tile of columns), the token's row in shared memory; a warp runs the
+//                    gate and up rows of four columns side by side (eight 16-byte loads in flight per lane).
 //   moe_pairs_down   out[t, c] = sum_j weight[t, j] * (Wd[e_j][c, :] . act[t * top_k + j, :]) in the order of j,
 //                    plus shared[t, c] * sigmoid(shared_gate[t]) when a shared expert's output is given.
 //   moe_sort         pairs counted per expert, offsets, and each pair's place in expert order (a stable
@@ -154,12 +155,21 @@ __device__ __forceinline__ float dot_row(const bf16* w, const float* x, int k, i
 
 #define MOE_COLS 32      // columns per block (8 warps, 4 columns a warp)
 
+// 8 bfloat16 weights (one 16-byte load) against 8 floats
+__device__ __forceinline__ float dot8(const uint4& u, const float4& xa, const float4& xb) {
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+    const float2 a = __bfloat1622float2(p[0]), b = __bfloat1622float2(p[1]), c = __bfloat1622float2(p[2]),
+                 e = __bfloat1622float2(p[3]);
+    return a.x * xa.x + a.y * xa.y + b.x * xa.z + b.y * xa.w + c.x * xb.x + c.y * xb.y + e.x * xb.z + e.y * xb.w;
+}
+__device__ __forceinline__ bool rows_vec_ok(const void* w, int k) { return (k & 7) == 0 && ((uintptr_t)w & 15) == 0; }
+
 // h [n, d]; w_gu [E][2F][d] (gate rows, then up rows); act [n * top_k, F]
 template <typename T>
 __global__ void __launch_bounds__(256)
 moe_pairs_gate_up_kernel(const T* h, const T* __restrict__ w_gu, const int* idx, T* act, int top_k, int d, int F,
                          GluForm glu) {
-    extern __shared__ float s_h[];
+    extern __shared__ __align__(16) float s_h[];
     pdl_wait();
     pdl_launch_dependents();
     const int pair = blockIdx.x, t = pair / top_k, e = idx[pair];
@@ -167,6 +177,44 @@ moe_pairs_gate_up_kernel(const T* h, const T* __restrict__ w_gu, const int* idx,
     for (int i = threadIdx.x; i < d; i += blockDim.x) s_h[i] = to_f<T>(h[(size_t)t * d + i]);
     __syncthreads();
     const T* wg = w_gu + (size_t)e * 2 * F * d;
+    if constexpr (sizeof(T) == 2) {
+        if (rows_vec_ok(wg, d)) {
+            // the warp's four columns at once: eight rows (gate and up), a 16-byte load of each in flight per lane
+            const T* rows[8];
+            int fcol[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                fcol[q] = blockIdx.y * MOE_COLS + warp + 8 * q;
+                const int fc = min(fcol[q], F - 1);
+                rows[q] = wg + (size_t)fc * d;
+                rows[4 + q] = wg + (size_t)(F + fc) * d;
+            }
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int i = lane * 8; i < d; i += 256) {
+                uint4 u[8];
+#pragma unroll
+                for (int r = 0; r < 8; ++r) u[r] = *reinterpret_cast<const uint4*>(rows[r] + i);
+                const float4 xa = *reinterpret_cast<const float4*>(s_h + i), xb = *reinterpret_cast<const float4*>(s_h + i + 4);
+#pragma unroll
+                for (int r = 0; r < 8; ++r) acc[r] += dot8(u[r], xa, xb);
+            }
+#pragma unroll
+            for (int r = 0; r < 8; ++r) acc[r] = warp_sum(acc[r]);
+            if (lane == 0) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    if (fcol[q] >= F) continue;
+                    float g = acc[q], u = acc[4 + q];
+                    if (glu.limit > 0.f) {
+                        g = fminf(g, glu.limit);
+                        u = fminf(fmaxf(u, -glu.limit), glu.limit);
+                    }
+                    act[(size_t)pair * F + fcol[q]] = from_f<T>(g / (1.0f + expf(-glu.alpha * g)) * (u + glu.shift));
+                }
+            }
+            return;
+        }
+    }
     for (int c = warp; c < MOE_COLS; c += 8) {
         const int f = blockIdx.y * MOE_COLS + c;
         if (f >= F) break;
@@ -189,13 +237,64 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 moe_pairs_down_kernel(const T* act, const T* __restrict__ w_down, const int* idx, const float* weight, float* out,
                       const float* shared, const float* gate, long long ld_gate, int top_k, int d, int F) {
-    extern __shared__ float s_a[];          // [top_k][F]
+    extern __shared__ __align__(16) float s_a[];          // [top_k][F]
     pdl_wait();
     pdl_launch_dependents();
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int i = threadIdx.x; i < top_k * F; i += blockDim.x) s_a[i] = to_f<T>(act[(size_t)t * top_k * F + i]);
     __syncthreads();
     const float sg = (shared && gate) ? 1.0f / (1.0f + expf(-gate[(size_t)t * ld_gate])) : 1.0f;
+    if constexpr (sizeof(T) == 2) {
+        if (rows_vec_ok(w_down, F)) {
+            // two of the warp's columns and four of the token's experts at once: eight 16-byte loads in flight per
+            // lane; a lane weights its partial sums in the order of j, one warp sum per column
+            for (int q0 = 0; q0 < 4; q0 += 2) {
+                const int col0 = blockIdx.y * MOE_COLS + warp + 8 * q0, col1 = col0 + 8;
+                if (col0 >= d) break;
+                const int c1 = min(col1, d - 1);
+                float tot0 = 0.f, tot1 = 0.f;
+                for (int j0 = 0; j0 < top_k; j0 += 4) {
+                    const T* rows[8];
+                    const float* xs[4];
+                    float wj[4];
+#pragma unroll
+                    for (int jj = 0; jj < 4; ++jj) {
+                        const int j = min(j0 + jj, top_k - 1);
+                        const int e = idx[(size_t)t * top_k + j];
+                        wj[jj] = j0 + jj < top_k ? weight[(size_t)t * top_k + j] : 0.f;
+                        rows[jj] = w_down + ((size_t)e * d + col0) * F;
+                        rows[4 + jj] = w_down + ((size_t)e * d + c1) * F;
+                        xs[jj] = s_a + (size_t)j * F;
+                    }
+                    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                    for (int i = lane * 8; i < F; i += 256) {
+                        uint4 u[8];
+#pragma unroll
+                        for (int r = 0; r < 8; ++r) u[r] = *reinterpret_cast<const uint4*>(rows[r] + i);
+#pragma unroll
+                        for (int jj = 0; jj < 4; ++jj) {
+                            const float4 xa = *reinterpret_cast<const float4*>(xs[jj] + i),
+                                         xb = *reinterpret_cast<const float4*>(xs[jj] + i + 4);
+                            acc[jj] += dot8(u[jj], xa, xb);
+                            acc[4 + jj] += dot8(u[4 + jj], xa, xb);
+                        }
+                    }
+#pragma unroll
+                    for (int jj = 0; jj < 4; ++jj) {
+                        tot0 += wj[jj] * acc[jj];
+                        tot1 += wj[jj] * acc[4 + jj];
+                    }
+                }
+                tot0 = warp_sum(tot0);
+                tot1 = warp_sum(tot1);
+                if (lane == 0) {
+                    out[(size_t)t * d + col0] = tot0 + (shared ? shared[(size_t)t * d + col0] * sg : 0.f);
+                    if (col1 < d) out[(size_t)t * d + col1] = tot1 + (shared ? shared[(size_t)t * d + col1] * sg : 0.f);
+                }
+            }
+            return;
+        }
+    }
     for (int c = warp; c < MOE_COLS; c += 8) {
         const int col = blockIdx.y * MOE_COLS + c;
         if (col >= d) break;
@@ -247,67 +346,284 @@ RLLM_API int rllm_moe_pairs_down(const void* act, const void* w_down, int dt, co
                        idx, weight, out, shared, gate, ld_gate, top_k, d, F);
 }
 
+// ------------------------------------------------------------------ experts, expert by expert (bfloat16, few rows)
+// The same sums as the pair kernels, but a block belongs to an expert: it lists the pairs that chose the
+// expert (in pair order), and runs MOE_TT of them side by side against each 16-byte piece of the expert's
+// rows, so an expert's matrices cross L2 once per MOE_TT of its tokens, not once per token, and an expert
+// that nobody chose costs a scan of idx.  A pair's sum is formed in the same order whatever else the list
+// holds.
+#define MOE_TT 4
+#define MOE_LIST 1024    // pairs of one expert a block can list (a token chooses an expert once: rows of the step)
+
+__device__ __forceinline__ int list_expert_pairs(const int* idx, int n_pairs, int e, int* s_list, int* s_n) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (warp == 0) {
+        int cnt = 0;
+        for (int p0 = 0; p0 < n_pairs; p0 += 32) {
+            const int p = p0 + lane;
+            const bool mine = p < n_pairs && idx[p] == e;
+            const unsigned m = __ballot_sync(0xffffffffu, mine);
+            const int at = cnt + __popc(m & ((1u << lane) - 1u));
+            if (mine && at < MOE_LIST) s_list[at] = p;
+            cnt += __popc(m);
+        }
+        if (lane == 0) *s_n = min(cnt, MOE_LIST);
+    }
+    __syncthreads();
+    return *s_n;
+}
+
+__device__ __forceinline__ void bf16x8_to_float(const uint4& u, float4& a, float4& b) {
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+    const float2 f0 = __bfloat1622float2(p[0]), f1 = __bfloat1622float2(p[1]), f2 = __bfloat1622float2(p[2]),
+                 f3 = __bfloat1622float2(p[3]);
+    a = make_float4(f0.x, f0.y, f1.x, f1.y);
+    b = make_float4(f2.x, f2.y, f3.x, f3.y);
+}
+
+// R rows of weights (16 bytes of each in flight per lane) against MOE_TT rows of x in shared memory (bfloat16, k apart)
+template <int R>
+__device__ __forceinline__ void rows_times_tokens(const bf16* const (&rows)[R], const bf16* s_x, int k, int lane,
+                                                  float (&acc)[R][MOE_TT]) {
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int tt = 0; tt < MOE_TT; ++tt) acc[r][tt] = 0.f;
+    for (int i = lane * 8; i < k; i += 256) {
+        uint4 u[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) u[r] = *reinterpret_cast<const uint4*>(rows[r] + i);
+#pragma unroll
+        for (int tt = 0; tt < MOE_TT; ++tt) {
+            float4 xa, xb;
+            bf16x8_to_float(*reinterpret_cast<const uint4*>(s_x + (size_t)tt * k + i), xa, xb);
+#pragma unroll
+            for (int r = 0; r < R; ++r) acc[r][tt] += dot8(u[r], xa, xb);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int tt = 0; tt < MOE_TT; ++tt) acc[r][tt] = warp_sum(acc[r][tt]);
+}
+
+// MOE_TT rows of k entries into shared memory: the rows src[row_of(c0 + tt)], the last one repeated past the list's end
+template <typename RowOf>
+__device__ __forceinline__ void stage_rows(bf16* s_x, const bf16* src, int k, int c0, int cnt, RowOf row_of) {
+    const int k8 = k >> 3;
+    for (int i = threadIdx.x; i < MOE_TT * k8; i += blockDim.x) {
+        const int tt = i / k8, c = i - tt * k8;
+        const size_t row = row_of(min(c0 + tt, cnt - 1));
+        reinterpret_cast<uint4*>(s_x)[i] = reinterpret_cast<const uint4*>(src + row * k)[c];
+    }
+}
+
+__global__ void __launch_bounds__(256)
+moe_expert_gate_up_kernel(const bf16* h, const bf16* __restrict__ w_gu, const int* idx, bf16* act, int n_pairs, int top_k,
+                          int d, int F, GluForm glu) {
+    extern __shared__ __align__(16) unsigned char s_raw[];
+    __shared__ int s_list[MOE_LIST];
+    __shared__ int s_n;
+    bf16* s_x = reinterpret_cast<bf16*>(s_raw);                           // [MOE_TT][d]
+    pdl_wait();
+    pdl_launch_dependents();
+    const int e = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int cnt = list_expert_pairs(idx, n_pairs, e, s_list, &s_n);
+    if (cnt == 0) return;
+    const bf16* wg = w_gu + (size_t)e * 2 * F * d;
+    const bf16* rows[8];
+    int fcol[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        fcol[q] = blockIdx.y * MOE_COLS + warp + 8 * q;
+        const int fc = min(fcol[q], F - 1);
+        rows[q] = wg + (size_t)fc * d;
+        rows[4 + q] = wg + (size_t)(F + fc) * d;
+    }
+    for (int c0 = 0; c0 < cnt; c0 += MOE_TT) {
+        __syncthreads();
+        stage_rows(s_x, h, d, c0, cnt, [&](int c) { return (size_t)(s_list[c] / top_k); });
+        __syncthreads();
+        float acc[8][MOE_TT];
+        rows_times_tokens<8>(rows, s_x, d, lane, acc);
+        if (lane == 0) {
+#pragma unroll
+            for (int tt = 0; tt < MOE_TT; ++tt) {
+                if (c0 + tt >= cnt) break;
+                const size_t pair = s_list[c0 + tt];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    if (fcol[q] >= F) continue;
+                    float g = acc[q][tt], u = acc[4 + q][tt];
+                    if (glu.limit > 0.f) {
+                        g = fminf(g, glu.limit);
+                        u = fminf(fmaxf(u, -glu.limit), glu.limit);
+                    }
+                    act[pair * F + fcol[q]] = from_f<bf16>(g / (1.0f + expf(-glu.alpha * g)) * (u + glu.shift));
+                }
+            }
+        }
+    }
+}
+
+#define MOE_DOWN_COLS 64     // columns per block of the down product (8 warps, 8 columns a warp)
+
+// y[pair, c] = Wd[e][c, :] . act[pair, :] for the pairs of the block's expert; moe_combine weights and adds them
+__global__ void __launch_bounds__(256)
+moe_expert_down_kernel(const bf16* act, const bf16* __restrict__ w_down, const int* idx, float* y, int n_pairs, int d,
+                       int F) {
+    extern __shared__ __align__(16) unsigned char s_raw[];
+    __shared__ int s_list[MOE_LIST];
+    __shared__ int s_n;
+    bf16* s_x = reinterpret_cast<bf16*>(s_raw);                           // [MOE_TT][F]
+    pdl_wait();
+    pdl_launch_dependents();
+    const int e = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int cnt = list_expert_pairs(idx, n_pairs, e, s_list, &s_n);
+    if (cnt == 0) return;
+    const bf16* rows[8];
+    int col[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+        col[q] = blockIdx.y * MOE_DOWN_COLS + warp + 8 * q;
+        rows[q] = w_down + ((size_t)e * d + min(col[q], d - 1)) * F;
+    }
+    for (int c0 = 0; c0 < cnt; c0 += MOE_TT) {
+        __syncthreads();
+        stage_rows(s_x, act, F, c0, cnt, [&](int c) { return (size_t)s_list[c]; });
+        __syncthreads();
+        float acc[8][MOE_TT];
+        rows_times_tokens<8>(rows, s_x, F, lane, acc);
+        if (lane == 0) {
+#pragma unroll
+            for (int tt = 0; tt < MOE_TT; ++tt) {
+                if (c0 + tt >= cnt) break;
+                const size_t pair = s_list[c0 + tt];
+#pragma unroll
+                for (int q = 0; q < 8; ++q)
+                    if (col[q] < d) y[pair * d + col[q]] = acc[q][tt];
+            }
+        }
+    }
+}
+
+static bool expert_kernels_fit(int n, int k) {
+    return n <= MOE_LIST && (k & 7) == 0 && (size_t)MOE_TT * k * sizeof(bf16) <= 48 * 1024;
+}
+
+RLLM_API int rllm_moe_expert_gate_up(const void* h, const void* w_gu, const int* idx, void* act, int n, int top_k, int E,
+                                     int d, int F, float limit, float alpha, float shift, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (d <= 0 || F <= 0 || top_k <= 0 || E <= 0 || !expert_kernels_fit(n, d) || ((uintptr_t)h & 15) || ((uintptr_t)w_gu & 15))
+        return (int)cudaErrorInvalidValue;
+    const GluForm glu = {limit, alpha, shift};
+    return rllm_launch(moe_expert_gate_up_kernel, dim3(E, (F + MOE_COLS - 1) / MOE_COLS), dim3(256),
+                       (size_t)MOE_TT * d * sizeof(bf16), stream, (const bf16*)h, (const bf16*)w_gu, idx, (bf16*)act,
+                       n * top_k, top_k, d, F, glu);
+}
+
+RLLM_API int rllm_moe_expert_down(const void* act, const void* w_down, const int* idx, float* y, int n, int top_k, int E,
+                                  int d, int F, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (d <= 0 || F <= 0 || top_k <= 0 || E <= 0 || !expert_kernels_fit(n, F) || ((uintptr_t)act & 15) ||
+        ((uintptr_t)w_down & 15))
+        return (int)cudaErrorInvalidValue;
+    return rllm_launch(moe_expert_down_kernel, dim3(E, (d + MOE_DOWN_COLS - 1) / MOE_DOWN_COLS), dim3(256),
+                       (size_t)MOE_TT * F * sizeof(bf16), stream, (const bf16*)act, (const bf16*)w_down, idx, y, n * top_k, d,
+                       F);
+}
+
 // ------------------------------------------------------------------ many rows: pairs in expert order
-// One block.  counts[e], offsets[e] (E + 1 entries) and place[pair]: the pair's row among all pairs sorted
-// by expert, pairs of one expert in pair order (stable), so the order never depends on scheduling.
+// counts[e], offsets[e] (E + 1 entries) and place[pair]: the pair's row among all pairs sorted by expert,
+// pairs of one expert in pair order (stable), so the order never depends on scheduling.  A block takes 32
+// experts, a warp one: every block counts all pairs (shared-memory atomics; integer sums have no order),
+// then a warp walks the pairs 32 at a time and ranks its expert's pairs by a ballot.
 __global__ void __launch_bounds__(1024)
-moe_sort_kernel(const int* idx, int n_pairs, int E, int* offsets, int* place) {
+moe_sort_kernel(const int* __restrict__ idx, int n_pairs, int E, int* offsets, int* place) {
     __shared__ int s_count[MOE_MAX_EXPERTS + 1];
     pdl_wait();
     pdl_launch_dependents();
-    const int tid = threadIdx.x;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     for (int e = tid; e <= E; e += blockDim.x) s_count[e] = 0;
     __syncthreads();
     for (int p = tid; p < n_pairs; p += blockDim.x) atomicAdd(&s_count[idx[p]], 1);
     __syncthreads();
-    if (tid == 0) {
+    if (warp == 0) {                                       // exclusive prefix sum over the experts, 32 at a time
         int run = 0;
-        for (int e = 0; e < E; ++e) {
-            const int c = s_count[e];
-            s_count[e] = run;
-            offsets[e] = run;
-            run += c;
+        for (int e0 = 0; e0 < E; e0 += 32) {
+            const int e = e0 + lane, c = e < E ? s_count[e] : 0;
+            int incl = c;
+#pragma unroll
+            for (int m = 1; m < 32; m <<= 1) {
+                const int up = __shfl_up_sync(0xffffffffu, incl, m);
+                if (lane >= m) incl += up;
+            }
+            if (e < E) s_count[e] = run + incl - c;
+            run += __shfl_sync(0xffffffffu, incl, 31);
         }
-        offsets[E] = run;
+        if (lane == 0) s_count[E] = run;
     }
     __syncthreads();
-    // a thread per expert walks the pairs in order: stable, and no atomics on the places
-    for (int e = tid; e < E; e += blockDim.x) {
-        if (offsets[e + 1] == offsets[e]) continue;
-        int at = offsets[e];
-        for (int p = 0; p < n_pairs; ++p)
-            if (idx[p] == e) place[p] = at++;
+    if (blockIdx.x == 0)
+        for (int e = tid; e <= E; e += blockDim.x) offsets[e] = s_count[e];
+    const int e = blockIdx.x * 32 + warp;
+    if (e >= E || s_count[e + 1] == s_count[e]) return;
+    int at = s_count[e];
+    for (int p0 = 0; p0 < n_pairs; p0 += 32) {
+        const int p = p0 + lane;
+        const bool mine = p < n_pairs && idx[p] == e;
+        const unsigned m = __ballot_sync(0xffffffffu, mine);
+        if (mine) place[p] = at + __popc(m & ((1u << lane) - 1u));
+        at += __popc(m);
     }
 }
 
 RLLM_API int rllm_moe_sort(const int* idx, int n_pairs, int E, int* offsets, int* place, cudaStream_t stream) {
     if (n_pairs <= 0) return 0;
     if (E <= 0 || E > MOE_MAX_EXPERTS) return (int)cudaErrorInvalidValue;
-    return rllm_launch(moe_sort_kernel, dim3(1), dim3(1024), 0, stream, idx, n_pairs, E, offsets, place);
+    return rllm_launch(moe_sort_kernel, dim3((E + 31) / 32), dim3(1024), 0, stream, idx, n_pairs, E, offsets, place);
 }
 
-// rows[place[pair]] = h[pair / top_k]
+// rows[place[pair]] = h[pair / top_k]: a block per token reads the row once (16 bytes a thread and turn where the
+// rows allow it) and writes it to the places of its top_k pairs
 template <typename T>
-__global__ void moe_gather_rows_kernel(const T* h, const int* place, T* rows, int top_k, int d) {
+__global__ void __launch_bounds__(256)
+moe_gather_rows_kernel(const T* h, const int* __restrict__ place, T* rows, int top_k, int d, int vec) {
     pdl_wait();
     pdl_launch_dependents();
-    const int pair = blockIdx.x;
-    const T* src = h + (size_t)(pair / top_k) * d;
-    T* dst = rows + (size_t)place[pair] * d;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = src[i];
+    const int t = blockIdx.x;
+    const T* src = h + (size_t)t * d;
+    if (vec) {
+        const int n16 = (int)((size_t)d * sizeof(T) / 16);
+        const uint4* s4 = reinterpret_cast<const uint4*>(src);
+        for (int i = threadIdx.x; i < n16; i += blockDim.x) {
+            const uint4 u = s4[i];
+            for (int j = 0; j < top_k; ++j)
+                reinterpret_cast<uint4*>(rows + (size_t)place[(size_t)t * top_k + j] * d)[i] = u;
+        }
+        return;
+    }
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const T v = src[i];
+        for (int j = 0; j < top_k; ++j) rows[(size_t)place[(size_t)t * top_k + j] * d + i] = v;
+    }
 }
 
 RLLM_API int rllm_moe_gather_rows(const void* h, int dt, const int* place, void* rows, int n_pairs, int top_k, int d,
                                   cudaStream_t stream) {
     if (n_pairs <= 0) return 0;
+    if (top_k <= 0 || n_pairs % top_k) return (int)cudaErrorInvalidValue;
+    const size_t row_bytes = (size_t)d * (dt == RLLM_F32 ? 4 : 2);
+    const int vec = row_bytes % 16 == 0 && ((uintptr_t)h & 15) == 0 && ((uintptr_t)rows & 15) == 0;
+    const dim3 grid(n_pairs / top_k), block(row_bytes >= 4096 ? 256 : 128);
     if (dt == RLLM_F32)
-        return rllm_launch(moe_gather_rows_kernel<float>, dim3(n_pairs), dim3(128), 0, stream, (const float*)h, place,
-                           (float*)rows, top_k, d);
-    return rllm_launch(moe_gather_rows_kernel<bf16>, dim3(n_pairs), dim3(128), 0, stream, (const bf16*)h, place,
-                       (bf16*)rows, top_k, d);
+        return rllm_launch(moe_gather_rows_kernel<float>, grid, block, 0, stream, (const float*)h, place, (float*)rows,
+                           top_k, d, vec);
+    return rllm_launch(moe_gather_rows_kernel<bf16>, grid, block, 0, stream, (const bf16*)h, place, (bf16*)rows, top_k, d,
+                       vec);
 }
 
-// out[t] = sum_j weight[t, j] * y[place[t * top_k + j]] (+ shared[t] * sigmoid(gate[t]))
+// out[t] = sum_j weight[t, j] * y[place[t * top_k + j]] (+ shared[t] * sigmoid(gate[t])); place null: y in pair order
 __global__ void moe_combine_kernel(const float* y, const int* place, const float* weight, float* out, const float* shared,
                                    const float* gate, long long ld_gate, int top_k, int d) {
     pdl_wait();
@@ -317,7 +633,7 @@ __global__ void moe_combine_kernel(const float* y, const int* place, const float
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
         float sum = 0.f;
         for (int j = 0; j < top_k; ++j)
-            sum += weight[(size_t)t * top_k + j] * y[(size_t)place[(size_t)t * top_k + j] * d + i];
+            sum += weight[(size_t)t * top_k + j] * y[(size_t)(place ? place[(size_t)t * top_k + j] : t * top_k + j) * d + i];
         out[(size_t)t * d + i] = sum + (shared ? shared[(size_t)t * d + i] * sg : 0.f);
     }
 }

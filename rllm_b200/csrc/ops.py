@@ -821,14 +821,32 @@ def moe_route(logits, correction, idx, weight, E, top_k, n_groups=1, keep_groups
     return idx, weight
 
 
+MOE_EXPERT_ROWS = 1024        # rows of a step the per-expert kernels can list (MOE_LIST in moe.cu)
+MOE_EXPERT_TOKENS = 4         # tokens of an expert side by side (MOE_TT)
+
+
+def _by_expert(x, n, k):
+    """Whether the few-row products run expert by expert (bfloat16, rows of a multiple of 8 entries that fit
+    the kernels' shared memory), not pair by pair."""
+    return (x.dtype == torch.bfloat16 and n <= MOE_EXPERT_ROWS and k % 8 == 0
+            and MOE_EXPERT_TOKENS * k * 2 <= 48 * 1024)
+
+
 def moe_pairs_gate_up(h, w_gu, idx, act, glu=(0.0, 1.0, 0.0)):
     """act[t * top_k + j] = glu(Wg[e] h[t], Wu[e] h[t]) with e = idx[t, j]; w_gu [E, 2F, d] (gate rows, then up
-    rows); h, w_gu, act of one type."""
+    rows); h, w_gu, act of one type.  bfloat16 rows that fit run expert by expert (an expert's matrices are
+    read once for four of its tokens), the rest pair by pair; each way sums in its own fixed order, and which
+    way runs depends on types and sizes only, never on the batch."""
     _need_cuda(h, w_gu, idx, act)
     _need_contig(h=h, w_gu=w_gu, idx=idx, act=act)
     n, d = h.shape
     top_k, F = idx.shape[1], act.shape[1]
     assert w_gu.shape[1:] == (2 * F, d) and act.shape == (n * top_k, F) and h.dtype == w_gu.dtype == act.dtype
+    if _by_expert(h, n, d):
+        _check(_lib("moe").rllm_moe_expert_gate_up(_ptr(h), _ptr(w_gu), _ptr(idx), _ptr(act), c_int(n), c_int(top_k),
+                                                   c_int(w_gu.shape[0]), c_int(d), c_int(F), c_float(glu[0]),
+                                                   c_float(glu[1]), c_float(glu[2]), _stream()), "moe_expert_gate_up")
+        return act
     _check(_lib("moe").rllm_moe_pairs_gate_up(_ptr(h), _ptr(w_gu), c_int(_code(h)), _ptr(idx), _ptr(act), c_int(n),
                                               c_int(top_k), c_int(d), c_int(F), c_float(glu[0]), c_float(glu[1]),
                                               c_float(glu[2]), _stream()), "moe_pairs_gate_up")
@@ -845,6 +863,11 @@ def moe_pairs_down(act, w_down, idx, weight, out, shared=None, gate=None):
     assert w_down.shape[1:] == (d, F) and act.shape == (n * top_k, F) and act.dtype == w_down.dtype
     assert out.dtype == torch.float32 and (shared is None or (shared.dtype == torch.float32 and shared.shape == (n, d)))
     assert gate is None or (gate.dtype == torch.float32 and gate.shape[0] == n)
+    if _by_expert(act, n, F):
+        y = torch.empty((n * top_k, d), dtype=torch.float32, device=out.device)
+        _check(_lib("moe").rllm_moe_expert_down(_ptr(act), _ptr(w_down), _ptr(idx), _ptr(y), c_int(n), c_int(top_k),
+                                                c_int(w_down.shape[0]), c_int(d), c_int(F), _stream()), "moe_expert_down")
+        return moe_combine(y, None, weight, out, shared, gate)
     if top_k * F * 4 > 96 * 1024:
         raise KernelError("moe_pairs_down: top_k * expert size exceeds the kernel's shared memory")
     _check(_lib("moe").rllm_moe_pairs_down(_ptr(act), _ptr(w_down), c_int(_code(act)), _ptr(idx), _ptr(weight), _ptr(out),
@@ -875,7 +898,8 @@ def moe_gather_rows(h, place, rows, top_k):
 
 
 def moe_combine(y, place, weight, out, shared=None, gate=None):
-    """out[t] = sum_j weight[t, j] * y[place[t * top_k + j]] (+ shared[t] * sigmoid(gate[t])), float32."""
+    """out[t] = sum_j weight[t, j] * y[place[t * top_k + j]] (+ shared[t] * sigmoid(gate[t])), float32;
+    place None: y holds the pairs in their own order."""
     _need_cuda(y, place, weight, out, shared, gate)
     _need_contig(y=y, place=place, weight=weight, out=out, shared=shared)
     n, d = out.shape

@@ -852,33 +852,31 @@ retention_kernel(const float* qp, const float* kp, const float* vp, const float*
 }
 
 // Between the passes: a request's segments in order, S_end = c^len * S_start + local end state, in place.
-template <int DKMAX>
-__global__ void __launch_bounds__(1024) retention_combine_kernel(const float* state, long long slot_stride, const int* __restrict__ slots,
-                                         const float* __restrict__ decay, int H, const TimeSegments seg) {
-    constexpr int IPT = DKMAX / RET_PARTS;
+// Every entry of the state goes its own way, so the entries of a head are spread over blockIdx.z: a
+// thread carries one entry through the request's segments.  per_head = DKMAX * dvp floats.
+#define RET_COMBINE_THREADS 256
+__global__ void __launch_bounds__(RET_COMBINE_THREADS)
+retention_combine_kernel(const float* state, long long slot_stride, const int* __restrict__ slots,
+                         const float* __restrict__ decay, int H, int per_head, const TimeSegments seg) {
     pdl_wait();
     pdl_launch_dependents();
-    const int tid = threadIdx.x, NT = blockDim.x, head = blockIdx.x, r = blockIdx.y;
+    const int head = blockIdx.x, r = blockIdx.y;
+    const int i = blockIdx.z * RET_COMBINE_THREADS + threadIdx.x;
     const int n = seg.req_items[r], item0 = seg.req_item0[r];
-    if (n < 2) return;
-    const size_t per_head = (size_t)DKMAX * (NT / RET_PARTS * 2);
-    const float* Sg = state + (size_t)slots[r] * slot_stride + (size_t)head * per_head;
-    float S[2 * IPT];
-    float* keep = seg.carry + ((size_t)(item0 + n - 1) * H + head) * per_head;    // the start state, for pass 2
-#pragma unroll
-    for (int ii = 0; ii < 2 * IPT; ++ii) {
-        S[ii] = Sg[(size_t)ii * NT + tid];
-        keep[(size_t)ii * NT + tid] = S[ii];
-    }
+    if (n < 2 || i >= per_head) return;
+    float S = state[(size_t)slots[r] * slot_stride + (size_t)head * per_head + i];
+    seg.carry[((size_t)(item0 + n - 1) * H + head) * per_head + i] = S;           // the start state, for pass 2
     const double c = (double)decay[head];
+    float w = 0.f;
+    int len = -1;
     for (int it = item0; it < item0 + n - 1; ++it) {
-        float* C = seg.carry + ((size_t)it * H + head) * per_head;
-        const float w = (float)pow(c, (double)(seg.t1[it] - seg.t0[it]));
-#pragma unroll
-        for (int ii = 0; ii < 2 * IPT; ++ii) {
-            S[ii] = w * S[ii] + C[(size_t)ii * NT + tid];
-            C[(size_t)ii * NT + tid] = S[ii];
+        float* C = seg.carry + ((size_t)it * H + head) * per_head + i;
+        if (seg.t1[it] - seg.t0[it] != len) {
+            len = seg.t1[it] - seg.t0[it];
+            w = (float)pow(c, (double)len);
         }
+        S = w * S + *C;
+        *C = S;
     }
 }
 
@@ -916,8 +914,9 @@ static int launch_retention(int n_requests, int threads, size_t smem, cudaStream
         return launch_retention_pass<TA, DKMAX, 0, MAXT>(dim3(H, n_requests), threads, smem, stream, RET_ARGS);
     int st = launch_retention_pass<TA, DKMAX, 1, MAXT>(dim3(H, seg.n_items), threads, smem, stream, RET_ARGS);
     if (st) return st;
-    st = rllm_launch(retention_combine_kernel<DKMAX>, dim3(H, n_requests), dim3(threads), 0, stream, (const float*)state,
-                     slot_stride, slots, decay, H, seg);
+    const int per_head = DKMAX * (threads / RET_PARTS * 2);
+    st = rllm_launch(retention_combine_kernel, dim3(H, n_requests, (per_head + RET_COMBINE_THREADS - 1) / RET_COMBINE_THREADS),
+                     dim3(RET_COMBINE_THREADS), 0, stream, (const float*)state, slot_stride, slots, decay, H, per_head, seg);
     if (st) return st;
     return launch_retention_pass<TA, DKMAX, 2, MAXT>(dim3(H, seg.n_items), threads, smem, stream, RET_ARGS);
 #undef RET_ARGS

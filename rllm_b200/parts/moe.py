@@ -19,7 +19,8 @@ correction, normalize, weight_eps, route_scale, shared_size, shared_gate.  Tenso
 router [E, d], correction [E], e<i>.gate, e<i>.up [F, d], e<i>.down [d, F], shared.gate, shared.up,
 shared.down, shared.sg [1, d].  Load-time transform: the experts' matrices are stacked ([E, 2F, d] gate
 rows then up rows, [E, d, F]), and the shared expert's gate row is stacked under the router's so that
-one product gives both.  The router's logits, scores, choice and weights are float32 in every mode.
+one product gives both (with rows of zeros up to a multiple of 8 rows).  The router's logits, scores, choice
+and weights are float32 in every mode.
 
 Steps of few rows run every (token, chosen expert) pair against its expert's matrices directly, with no
 host involvement (so such steps can be captured into graphs).  Steps of many rows sort the pairs by
@@ -82,6 +83,9 @@ class RoutedExperts(FeedForward):
         router = [tensors[p + "router"].to(dt)]
         if self.shared_gate:
             router.append(tensors[p + "shared.sg"].to(dt).reshape(1, -1))
+        rows = sum(r.shape[0] for r in router)
+        if rows % 8:                # rows of zeros up to a multiple of 8: the logits' rows are then aligned for every product kernel
+            router.append(torch.zeros((8 - rows % 8, self.hidden_size), dtype=dt, device=router[0].device))
         self.w_router = self._to_device(torch.cat(router, 0))
         if self.has_correction:
             self.correction = self._to_device(tensors[p + "correction"], torch.float32)
@@ -94,7 +98,7 @@ class RoutedExperts(FeedForward):
             self.w_shared_down = self._to_device(tensors[p + "shared.down"])
 
     def route(self, h):
-        """(idx int32 [n, top_k], weight float32 [n, top_k], logits float32 [n, E (+ 1)])."""
+        """(idx int32 [n, top_k], weight float32 [n, top_k], logits float32 [n, E (+ 1), padded to a multiple of 8])."""
         n, dev = h.shape[0], h.device
         logits = ops.linear(h, self.w_router, out_dtype=torch.float32)
         idx = torch.empty((n, self.top_k), dtype=torch.int32, device=dev)
@@ -111,7 +115,7 @@ class RoutedExperts(FeedForward):
             act = torch.empty((n, self.shared_size), dtype=dt, device=dev)
             ops.gate_up_swiglu(h, self.w_shared_gu, act)
             shared = ops.linear(act, self.w_shared_down, out_dtype=torch.float32)
-            gate = logits[:, self.E:] if self.shared_gate else None
+            gate = logits[:, self.E:self.E + 1] if self.shared_gate else None
         out = torch.empty((n, d), dtype=torch.float32, device=dev)
         if n <= PAIR_ROWS or torch.cuda.is_current_stream_capturing():
             act = torch.empty((n * self.top_k, self.F), dtype=dt, device=dev)

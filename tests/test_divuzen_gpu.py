@@ -353,7 +353,7 @@ def test_router_kernel(E, top, count, keep):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("n", [1, 9, 150])
+@pytest.mark.parametrize("n", [1, 9, 37, 150])
 def test_routed_experts_part(dtype, n):
     """The feed-forward part alone, on few rows (every pair against its expert's matrices) and on many
     (pairs sorted by expert, each expert's rows through the products): against the plain sum."""
