@@ -347,12 +347,17 @@ RLLM_API int rllm_moe_pairs_down(const void* act, const void* w_down, int dt, co
 }
 
 // ------------------------------------------------------------------ experts, expert by expert (bfloat16, few rows)
-// The same sums as the pair kernels, but a block belongs to an expert: it lists the pairs that chose the
-// expert (in pair order), and runs MOE_TT of them side by side against each 16-byte piece of the expert's
-// rows, so an expert's matrices cross L2 once per MOE_TT of its tokens, not once per token, and an expert
-// that nobody chose costs a scan of idx.  A pair's sum is formed in the same order whatever else the list
-// holds.
-#define MOE_TT 4
+// The same products on the tensor cores, with a block per (expert, tile of columns): the block lists the pairs
+// that chose its expert (in pair order) and runs them eight at a time as the n side of mma.sync m16n8k16, the
+// expert's rows as the m side.  An expert's matrices are read once per eight of its tokens, straight from
+// global memory into the A fragments (no conversion, no shared memory); an expert that nobody chose costs a
+// scan of idx.  A token's sums are formed in the same order whatever else the list holds.
+//
+// Fragments without ldmatrix: within a step of 32 k, lane (g = lane / 4, c = lane % 4) loads the 16 bytes
+// [8c, 8c + 8) of rows g and g + 8 and of token g.  A dot product does not care in which order k is walked as
+// long as both operands walk alike, so the first four bytes of each load serve as the k pair (2c, 2c + 1) of
+// one mma, the next four as its pair (2c + 8, 2c + 9), and the second half of the load feeds a second mma.
+#define MOE_MT 8         // tokens of an expert side by side (n of the mma)
 #define MOE_LIST 1024    // pairs of one expert a block can list (a token chooses an expert once: rows of the step)
 
 __device__ __forceinline__ int list_expert_pairs(const int* idx, int n_pairs, int e, int* s_list, int* s_n) {
@@ -373,143 +378,116 @@ __device__ __forceinline__ int list_expert_pairs(const int* idx, int n_pairs, in
     return *s_n;
 }
 
-__device__ __forceinline__ void bf16x8_to_float(const uint4& u, float4& a, float4& b) {
-    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
-    const float2 f0 = __bfloat1622float2(p[0]), f1 = __bfloat1622float2(p[1]), f2 = __bfloat1622float2(p[2]),
-                 f3 = __bfloat1622float2(p[3]);
-    a = make_float4(f0.x, f0.y, f1.x, f1.y);
-    b = make_float4(f2.x, f2.y, f3.x, f3.y);
+__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                          uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// R rows of weights (16 bytes of each in flight per lane) against MOE_TT rows of x in shared memory (bfloat16, k apart)
-template <int R>
-__device__ __forceinline__ void rows_times_tokens(const bf16* const (&rows)[R], const bf16* s_x, int k, int lane,
-                                                  float (&acc)[R][MOE_TT]) {
+// Rows lo (this lane's row g) and hi (row g + 8) of k entries against the lane's token row x: acc[0], acc[1] = row g
+// times tokens 2c and 2c + 1, acc[2], acc[3] = row g + 8 times the same.  Four steps of 32 k in flight (eight
+// 16-byte loads of weights a lane); two accumulators take turns and are added at the end.
+__device__ __forceinline__ void rows16_times_tokens8(const bf16* lo, const bf16* hi, const bf16* x, int k, int c,
+                                                     float (&acc)[4]) {
+    float a0[4] = {0.f, 0.f, 0.f, 0.f}, a1[4] = {0.f, 0.f, 0.f, 0.f};
+    const int off = 8 * c;
+    int k0 = 0;
+    for (; k0 + 128 <= k; k0 += 128) {
+        uint4 v[4], w[4], xb[4];
 #pragma unroll
-    for (int r = 0; r < R; ++r)
+        for (int s = 0; s < 4; ++s) {
+            v[s] = *reinterpret_cast<const uint4*>(lo + k0 + 32 * s + off);
+            w[s] = *reinterpret_cast<const uint4*>(hi + k0 + 32 * s + off);
+        }
 #pragma unroll
-        for (int tt = 0; tt < MOE_TT; ++tt) acc[r][tt] = 0.f;
-    for (int i = lane * 8; i < k; i += 256) {
-        uint4 u[R];
+        for (int s = 0; s < 4; ++s) xb[s] = *reinterpret_cast<const uint4*>(x + k0 + 32 * s + off);
 #pragma unroll
-        for (int r = 0; r < R; ++r) u[r] = *reinterpret_cast<const uint4*>(rows[r] + i);
-#pragma unroll
-        for (int tt = 0; tt < MOE_TT; ++tt) {
-            float4 xa, xb;
-            bf16x8_to_float(*reinterpret_cast<const uint4*>(s_x + (size_t)tt * k + i), xa, xb);
-#pragma unroll
-            for (int r = 0; r < R; ++r) acc[r][tt] += dot8(u[r], xa, xb);
+        for (int s = 0; s < 4; ++s) {
+            mma_16816(a0, v[s].x, w[s].x, v[s].y, w[s].y, xb[s].x, xb[s].y);
+            mma_16816(a1, v[s].z, w[s].z, v[s].w, w[s].w, xb[s].z, xb[s].w);
         }
     }
-#pragma unroll
-    for (int r = 0; r < R; ++r)
-#pragma unroll
-        for (int tt = 0; tt < MOE_TT; ++tt) acc[r][tt] = warp_sum(acc[r][tt]);
-}
-
-// MOE_TT rows of k entries into shared memory: the rows src[row_of(c0 + tt)], the last one repeated past the list's end
-template <typename RowOf>
-__device__ __forceinline__ void stage_rows(bf16* s_x, const bf16* src, int k, int c0, int cnt, RowOf row_of) {
-    const int k8 = k >> 3;
-    for (int i = threadIdx.x; i < MOE_TT * k8; i += blockDim.x) {
-        const int tt = i / k8, c = i - tt * k8;
-        const size_t row = row_of(min(c0 + tt, cnt - 1));
-        reinterpret_cast<uint4*>(s_x)[i] = reinterpret_cast<const uint4*>(src + row * k)[c];
+    for (; k0 < k; k0 += 32) {
+        uint4 v = make_uint4(0u, 0u, 0u, 0u), w = v, xb = v;
+        if (k0 + off < k) {
+            v = *reinterpret_cast<const uint4*>(lo + k0 + off);
+            w = *reinterpret_cast<const uint4*>(hi + k0 + off);
+            xb = *reinterpret_cast<const uint4*>(x + k0 + off);
+        }
+        mma_16816(a0, v.x, w.x, v.y, w.y, xb.x, xb.y);
+        mma_16816(a1, v.z, w.z, v.w, w.w, xb.z, xb.w);
     }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[i] = a0[i] + a1[i];
 }
 
-__global__ void __launch_bounds__(256)
+// 4 warps; a warp takes 8 columns: their gate rows are rows 0..7 of its mma, their up rows rows 8..15, so a
+// lane ends up with gate and up of one column for two tokens.
+__global__ void __launch_bounds__(128)
 moe_expert_gate_up_kernel(const bf16* h, const bf16* __restrict__ w_gu, const int* idx, bf16* act, int n_pairs, int top_k,
                           int d, int F, GluForm glu) {
-    extern __shared__ __align__(16) unsigned char s_raw[];
     __shared__ int s_list[MOE_LIST];
     __shared__ int s_n;
-    bf16* s_x = reinterpret_cast<bf16*>(s_raw);                           // [MOE_TT][d]
     pdl_wait();
     pdl_launch_dependents();
-    const int e = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
     const int cnt = list_expert_pairs(idx, n_pairs, e, s_list, &s_n);
     if (cnt == 0) return;
+    const int f = blockIdx.y * MOE_COLS + warp * 8 + g;
     const bf16* wg = w_gu + (size_t)e * 2 * F * d;
-    const bf16* rows[8];
-    int fcol[4];
+    const bf16* lo = wg + (size_t)min(f, F - 1) * d;
+    const bf16* hi = wg + (size_t)(F + min(f, F - 1)) * d;
+    for (int c0 = 0; c0 < cnt; c0 += MOE_MT) {
+        const int mine = s_list[min(c0 + g, cnt - 1)];                     // the token this lane loads for the n side
+        float acc[4];
+        rows16_times_tokens8(lo, hi, h + (size_t)(mine / top_k) * d, d, c, acc);
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        fcol[q] = blockIdx.y * MOE_COLS + warp + 8 * q;
-        const int fc = min(fcol[q], F - 1);
-        rows[q] = wg + (size_t)fc * d;
-        rows[4 + q] = wg + (size_t)(F + fc) * d;
-    }
-    for (int c0 = 0; c0 < cnt; c0 += MOE_TT) {
-        __syncthreads();
-        stage_rows(s_x, h, d, c0, cnt, [&](int c) { return (size_t)(s_list[c] / top_k); });
-        __syncthreads();
-        float acc[8][MOE_TT];
-        rows_times_tokens<8>(rows, s_x, d, lane, acc);
-        if (lane == 0) {
-#pragma unroll
-            for (int tt = 0; tt < MOE_TT; ++tt) {
-                if (c0 + tt >= cnt) break;
-                const size_t pair = s_list[c0 + tt];
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    if (fcol[q] >= F) continue;
-                    float g = acc[q][tt], u = acc[4 + q][tt];
-                    if (glu.limit > 0.f) {
-                        g = fminf(g, glu.limit);
-                        u = fminf(fmaxf(u, -glu.limit), glu.limit);
-                    }
-                    act[pair * F + fcol[q]] = from_f<bf16>(g / (1.0f + expf(-glu.alpha * g)) * (u + glu.shift));
-                }
+        for (int q = 0; q < 2; ++q) {
+            const int at = c0 + 2 * c + q;
+            if (at >= cnt || f >= F) continue;
+            float gv = acc[q], uv = acc[2 + q];
+            if (glu.limit > 0.f) {
+                gv = fminf(gv, glu.limit);
+                uv = fminf(fmaxf(uv, -glu.limit), glu.limit);
             }
+            act[(size_t)s_list[at] * F + f] = from_f<bf16>(gv / (1.0f + expf(-glu.alpha * gv)) * (uv + glu.shift));
         }
     }
 }
 
-#define MOE_DOWN_COLS 64     // columns per block of the down product (8 warps, 8 columns a warp)
+#define MOE_DOWN_COLS 64     // columns per block of the down product (4 warps, 16 columns a warp)
 
-// y[pair, c] = Wd[e][c, :] . act[pair, :] for the pairs of the block's expert; moe_combine weights and adds them
-__global__ void __launch_bounds__(256)
+// y[pair, col] = Wd[e][col, :] . act[pair, :] for the pairs of the block's expert; moe_combine weights and adds them
+__global__ void __launch_bounds__(128)
 moe_expert_down_kernel(const bf16* act, const bf16* __restrict__ w_down, const int* idx, float* y, int n_pairs, int d,
                        int F) {
-    extern __shared__ __align__(16) unsigned char s_raw[];
     __shared__ int s_list[MOE_LIST];
     __shared__ int s_n;
-    bf16* s_x = reinterpret_cast<bf16*>(s_raw);                           // [MOE_TT][F]
     pdl_wait();
     pdl_launch_dependents();
-    const int e = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
     const int cnt = list_expert_pairs(idx, n_pairs, e, s_list, &s_n);
     if (cnt == 0) return;
-    const bf16* rows[8];
-    int col[8];
+    const int col_lo = blockIdx.y * MOE_DOWN_COLS + warp * 16 + g, col_hi = col_lo + 8;
+    const bf16* lo = w_down + ((size_t)e * d + min(col_lo, d - 1)) * F;
+    const bf16* hi = w_down + ((size_t)e * d + min(col_hi, d - 1)) * F;
+    for (int c0 = 0; c0 < cnt; c0 += MOE_MT) {
+        const int mine = s_list[min(c0 + g, cnt - 1)];
+        float acc[4];
+        rows16_times_tokens8(lo, hi, act + (size_t)mine * F, F, c, acc);
 #pragma unroll
-    for (int q = 0; q < 8; ++q) {
-        col[q] = blockIdx.y * MOE_DOWN_COLS + warp + 8 * q;
-        rows[q] = w_down + ((size_t)e * d + min(col[q], d - 1)) * F;
-    }
-    for (int c0 = 0; c0 < cnt; c0 += MOE_TT) {
-        __syncthreads();
-        stage_rows(s_x, act, F, c0, cnt, [&](int c) { return (size_t)s_list[c]; });
-        __syncthreads();
-        float acc[8][MOE_TT];
-        rows_times_tokens<8>(rows, s_x, F, lane, acc);
-        if (lane == 0) {
-#pragma unroll
-            for (int tt = 0; tt < MOE_TT; ++tt) {
-                if (c0 + tt >= cnt) break;
-                const size_t pair = s_list[c0 + tt];
-#pragma unroll
-                for (int q = 0; q < 8; ++q)
-                    if (col[q] < d) y[pair * d + col[q]] = acc[q][tt];
-            }
+        for (int q = 0; q < 2; ++q) {
+            const int at = c0 + 2 * c + q;
+            if (at >= cnt) continue;
+            const size_t pair = s_list[at];
+            if (col_lo < d) y[pair * d + col_lo] = acc[q];
+            if (col_hi < d) y[pair * d + col_hi] = acc[2 + q];
         }
     }
 }
 
-static bool expert_kernels_fit(int n, int k) {
-    return n <= MOE_LIST && (k & 7) == 0 && (size_t)MOE_TT * k * sizeof(bf16) <= 48 * 1024;
-}
+static bool expert_kernels_fit(int n, int k) { return n <= MOE_LIST && (k & 7) == 0; }
 
 RLLM_API int rllm_moe_expert_gate_up(const void* h, const void* w_gu, const int* idx, void* act, int n, int top_k, int E,
                                      int d, int F, float limit, float alpha, float shift, cudaStream_t stream) {
@@ -517,9 +495,8 @@ RLLM_API int rllm_moe_expert_gate_up(const void* h, const void* w_gu, const int*
     if (d <= 0 || F <= 0 || top_k <= 0 || E <= 0 || !expert_kernels_fit(n, d) || ((uintptr_t)h & 15) || ((uintptr_t)w_gu & 15))
         return (int)cudaErrorInvalidValue;
     const GluForm glu = {limit, alpha, shift};
-    return rllm_launch(moe_expert_gate_up_kernel, dim3(E, (F + MOE_COLS - 1) / MOE_COLS), dim3(256),
-                       (size_t)MOE_TT * d * sizeof(bf16), stream, (const bf16*)h, (const bf16*)w_gu, idx, (bf16*)act,
-                       n * top_k, top_k, d, F, glu);
+    return rllm_launch(moe_expert_gate_up_kernel, dim3(E, (F + MOE_COLS - 1) / MOE_COLS), dim3(128), 0, stream,
+                       (const bf16*)h, (const bf16*)w_gu, idx, (bf16*)act, n * top_k, top_k, d, F, glu);
 }
 
 RLLM_API int rllm_moe_expert_down(const void* act, const void* w_down, const int* idx, float* y, int n, int top_k, int E,
@@ -528,9 +505,8 @@ RLLM_API int rllm_moe_expert_down(const void* act, const void* w_down, const int
     if (d <= 0 || F <= 0 || top_k <= 0 || E <= 0 || !expert_kernels_fit(n, F) || ((uintptr_t)act & 15) ||
         ((uintptr_t)w_down & 15))
         return (int)cudaErrorInvalidValue;
-    return rllm_launch(moe_expert_down_kernel, dim3(E, (d + MOE_DOWN_COLS - 1) / MOE_DOWN_COLS), dim3(256),
-                       (size_t)MOE_TT * F * sizeof(bf16), stream, (const bf16*)act, (const bf16*)w_down, idx, y, n * top_k, d,
-                       F);
+    return rllm_launch(moe_expert_down_kernel, dim3(E, (d + MOE_DOWN_COLS - 1) / MOE_DOWN_COLS), dim3(128), 0, stream,
+                       (const bf16*)act, (const bf16*)w_down, idx, y, n * top_k, d, F);
 }
 
 // ------------------------------------------------------------------ many rows: pairs in expert order
@@ -624,30 +600,64 @@ RLLM_API int rllm_moe_gather_rows(const void* h, int dt, const int* place, void*
 }
 
 // out[t] = sum_j weight[t, j] * y[place[t * top_k + j]] (+ shared[t] * sigmoid(gate[t])); place null: y in pair order
-__global__ void moe_combine_kernel(const float* y, const int* place, const float* weight, float* out, const float* shared,
-                                   const float* gate, long long ld_gate, int top_k, int d) {
+// A thread takes four neighbouring columns where the rows allow it (16-byte loads, a token's top_k rows in flight
+// side by side), one column otherwise; the columns of a token are spread over blockIdx.y.
+template <int VEC>
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const float* y, const int* place, const float* weight, float* out, const float* shared,
+                   const float* gate, long long ld_gate, int top_k, int d) {
     pdl_wait();
     pdl_launch_dependents();
     const int t = blockIdx.x;
+    const int i = (blockIdx.y * blockDim.x + threadIdx.x) * VEC;
+    if (i >= d) return;
     const float sg = (shared && gate) ? 1.0f / (1.0f + expf(-gate[(size_t)t * ld_gate])) : 1.0f;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) {
-        float sum = 0.f;
-        for (int j = 0; j < top_k; ++j)
-            sum += weight[(size_t)t * top_k + j] * y[(size_t)(place ? place[(size_t)t * top_k + j] : t * top_k + j) * d + i];
-        out[(size_t)t * d + i] = sum + (shared ? shared[(size_t)t * d + i] * sg : 0.f);
+    float sum[VEC];
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) sum[v] = 0.f;
+#pragma unroll 4
+    for (int j = 0; j < top_k; ++j) {
+        const float w = weight[(size_t)t * top_k + j];
+        const float* row = y + (size_t)(place ? place[(size_t)t * top_k + j] : t * top_k + j) * d + i;
+        if constexpr (VEC == 4) {
+            const float4 r = *reinterpret_cast<const float4*>(row);
+            sum[0] += w * r.x;
+            sum[1] += w * r.y;
+            sum[2] += w * r.z;
+            sum[3] += w * r.w;
+        } else {
+            sum[0] += w * row[0];
+        }
+    }
+    if constexpr (VEC == 4) {
+        float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (shared) s4 = *reinterpret_cast<const float4*>(shared + (size_t)t * d + i);
+        *reinterpret_cast<float4*>(out + (size_t)t * d + i) =
+            make_float4(sum[0] + s4.x * sg, sum[1] + s4.y * sg, sum[2] + s4.z * sg, sum[3] + s4.w * sg);
+    } else {
+        out[(size_t)t * d + i] = sum[0] + (shared ? shared[(size_t)t * d + i] * sg : 0.f);
     }
 }
 
 RLLM_API int rllm_moe_combine(const float* y, const int* place, const float* weight, float* out, const float* shared,
                               const float* gate, long long ld_gate, int n, int top_k, int d, cudaStream_t stream) {
     if (n <= 0) return 0;
-    return rllm_launch(moe_combine_kernel, dim3(n), dim3(d >= 1024 ? 256 : 128), 0, stream, y, place, weight, out, shared,
-                       gate, ld_gate, top_k, d);
+    const auto al16 = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+    if ((d & 3) == 0 && al16(y) && al16(out) && al16(shared)) {
+        const int threads = d >= 1024 ? 256 : 128;
+        return rllm_launch(moe_combine_kernel<4>, dim3(n, (d / 4 + threads - 1) / threads), dim3(threads), 0, stream, y,
+                           place, weight, out, shared, gate, ld_gate, top_k, d);
+    }
+    const int threads = d >= 256 ? 256 : 128;
+    return rllm_launch(moe_combine_kernel<1>, dim3(n, (d + threads - 1) / threads), dim3(threads), 0, stream, y, place,
+                       weight, out, shared, gate, ld_gate, top_k, d);
 }
 
 RLLM_PACKED(rllm_moe_route)
 RLLM_PACKED(rllm_moe_pairs_gate_up)
 RLLM_PACKED(rllm_moe_pairs_down)
+RLLM_PACKED(rllm_moe_expert_gate_up)
+RLLM_PACKED(rllm_moe_expert_down)
 RLLM_PACKED(rllm_moe_sort)
 RLLM_PACKED(rllm_moe_gather_rows)
 RLLM_PACKED(rllm_moe_combine)

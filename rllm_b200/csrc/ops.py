@@ -822,20 +822,18 @@ def moe_route(logits, correction, idx, weight, E, top_k, n_groups=1, keep_groups
 
 
 MOE_EXPERT_ROWS = 1024        # rows of a step the per-expert kernels can list (MOE_LIST in moe.cu)
-MOE_EXPERT_TOKENS = 4         # tokens of an expert side by side (MOE_TT)
 
 
 def _by_expert(x, n, k):
-    """Whether the few-row products run expert by expert (bfloat16, rows of a multiple of 8 entries that fit
-    the kernels' shared memory), not pair by pair."""
-    return (x.dtype == torch.bfloat16 and n <= MOE_EXPERT_ROWS and k % 8 == 0
-            and MOE_EXPERT_TOKENS * k * 2 <= 48 * 1024)
+    """Whether the few-row products run expert by expert on the tensor cores (bfloat16, rows of a multiple
+    of 8 entries), not pair by pair."""
+    return x.dtype == torch.bfloat16 and n <= MOE_EXPERT_ROWS and k % 8 == 0
 
 
 def moe_pairs_gate_up(h, w_gu, idx, act, glu=(0.0, 1.0, 0.0)):
     """act[t * top_k + j] = glu(Wg[e] h[t], Wu[e] h[t]) with e = idx[t, j]; w_gu [E, 2F, d] (gate rows, then up
     rows); h, w_gu, act of one type.  bfloat16 rows that fit run expert by expert (an expert's matrices are
-    read once for four of its tokens), the rest pair by pair; each way sums in its own fixed order, and which
+    read once for eight of its tokens), the rest pair by pair; each way sums in its own fixed order, and which
     way runs depends on types and sizes only, never on the batch."""
     _need_cuda(h, w_gu, idx, act)
     _need_contig(h=h, w_gu=w_gu, idx=idx, act=act)
