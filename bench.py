@@ -160,7 +160,7 @@ def divuzen_shape(width: int) -> dict:
     moe = {"kind": "moe", "expert": {"ff": 3 * width // 8}, "shared": {"ff": 3 * width // 4},
            "router": {"experts": 16, "top": 4, "scale": 2.5, "groups": {"count": 4, "keep": 2}}}
     ret = {"heads": rh, "dim": 128, "vdim": 256, "rot": {"dims": 128, "base": 1000000.0},
-           "decay": [1.0 - 2.0 ** (-5.0 - 5.0 * i / max(1, rh - 1)) for i in range(rh)]}
+           "decay": [1.0 - 2.0 ** (-4.0 - 6.5 * i / max(1, rh - 1)) for i in range(rh)]}
     att = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "rot": {"dims": 64, "base": 10000.0},
            "scale": 128 ** -0.5}
     layers = []
@@ -226,7 +226,7 @@ def falalix_compare(a):
                 if a.profile == "prefill":
                     eng.step([StepItem("p", prompts[0], [PROMPT - 1])])
                 else:
-                    eng.step([StepItem(b, [7], [0]) for b in range(a.batch)])
+                    eng.step([StepItem(b, [(7 + 101 * b) % V], [0]) for b in range(a.batch)])   # unlike tokens: routed layers spread
                 torch.cuda.synchronize()
                 torch.cuda.profiler.stop()
                 print(f"profiled one {a.profile} step of the {family} shape {size}")
