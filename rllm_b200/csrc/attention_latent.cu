@@ -62,6 +62,7 @@ struct LatentParams {
     int* err;
     int H, W, V, bs, split;
     float scale, softcap;
+    int window;               // > 0: a token sees only the last `window` keys (itself included)
 };
 
 __device__ __forceinline__ uint32_t lat_pack(float lo, float hi) {
@@ -79,7 +80,10 @@ __global__ void __launch_bounds__(128) latent_decode_kernel(const LatentParams p
     const int head0 = hc * LAT_HEADS;
     const size_t part = ((size_t)tok * gridDim.y + hc) * gridDim.z + z;
     const int pos = p.positions[tok];
-    const int kb = z * p.split, ke = min(pos + 1, kb + p.split);
+    // with a window the splits count from the window's first key rounded down to a tile, so that the
+    // number of splits follows the window and not the context
+    const int lo = p.window > 0 ? max(pos + 1 - p.window, 0) : 0;
+    const int kb = lo / LAT_TILE * LAT_TILE + z * p.split, ke = min(pos + 1, kb + p.split);
     pdl_wait();
     if (kb >= ke) {                                                 // an empty split
         if (tid < LAT_HEADS) {
@@ -172,7 +176,8 @@ __global__ void __launch_bounds__(128) latent_decode_kernel(const LatentParams p
             for (int e = 0; e < 4; ++e) {
                 float v = s[j][e] * p.scale;
                 if (p.softcap > 0.f) v = p.softcap * tanhf(v / p.softcap);
-                if (kt + j * 8 + 2 * t4 + (e & 1) >= ke) v = -INFINITY;
+                const int key = kt + j * 8 + 2 * t4 + (e & 1);
+                if (key >= ke || key < lo) v = -INFINITY;
                 s[j][e] = v;
                 mx[e >> 1] = fmaxf(mx[e >> 1], v);
             }
@@ -181,7 +186,7 @@ __global__ void __launch_bounds__(128) latent_decode_kernel(const LatentParams p
         for (int x = 0; x < 2; ++x) {
             mx[x] = fmaxf(mx[x], __shfl_xor_sync(0xffffffffu, mx[x], 1));
             mx[x] = fmaxf(mx[x], __shfl_xor_sync(0xffffffffu, mx[x], 2));
-            const float m_new = fmaxf(m_run[x], mx[x]);                // finite: the tile's first key is live
+            const float m_new = fmaxf(m_run[x], mx[x]);                // finite: every tile of a split holds a live key
             alpha[x] = expf(m_run[x] - m_new);                         // 0 at the first tile
             m_run[x] = m_new;
         }
@@ -307,15 +312,15 @@ static size_t latent_smem(int W) {
 
 // q [n, H * W], cache [pages, 1, bs, W], out [n, H * V] (all bfloat16); part_o needs n * chunks * n_splits
 // * 32 * V floats, part_ml the same with 2 in place of V (chunks = ceil(H / 32)); n_splits * split_keys
-// must cover the longest context; split_keys a multiple of 32.
+// must cover the longest context (with a window: the window and one tile); split_keys a multiple of 32.
 RLLM_API int rllm_latent_decode_attention(const void* q, const void* cache, void* out, float* part_o, float* part_ml,
                                           const int* positions, const int* seq_ids, const int* block_table,
                                           int table_stride, int n, int H, int W, int V, int bs, float scale,
                                           float softcap, int split_keys, int n_splits, long long n_pages, int* err,
-                                          cudaStream_t stream) {
+                                          int window, cudaStream_t stream) {
     if (n <= 0) return 0;
     if (H <= 0 || W % 16 || V % 64 || V <= 0 || V > 16 * LAT_MAX_NT || V > W || bs <= 0 || split_keys <= 0 ||
-        split_keys % LAT_TILE || n_splits <= 0 || n_splits > 8192 || !part_o || !part_ml || softcap < 0.f)
+        split_keys % LAT_TILE || n_splits <= 0 || n_splits > 8192 || !part_o || !part_ml || softcap < 0.f || window < 0)
         return (int)cudaErrorInvalidValue;
     const size_t smem = latent_smem(W);
     if (smem > 227 * 1024) return (int)cudaErrorInvalidValue;
@@ -329,7 +334,7 @@ RLLM_API int rllm_latent_decode_attention(const void* q, const void* cache, void
     p.q = (const bf16*)q; p.cache = (const bf16*)cache; p.part_o = part_o; p.part_ml = part_ml;
     p.positions = positions; p.seq_ids = seq_ids; p.block_table = block_table; p.table_stride = table_stride;
     p.n_pages = (int)(n_pages > 0x7fffffffLL ? 0x7fffffffLL : n_pages); p.err = err;
-    p.H = H; p.W = W; p.V = V; p.bs = bs; p.split = split_keys; p.scale = scale; p.softcap = softcap;
+    p.H = H; p.W = W; p.V = V; p.bs = bs; p.split = split_keys; p.scale = scale; p.softcap = softcap; p.window = window;
     const int chunks = (H + LAT_HEADS - 1) / LAT_HEADS;
     int st = rllm_launch(latent_decode_kernel, dim3(n, chunks, n_splits), dim3(128), smem, stream, p);
     if (st) return st;

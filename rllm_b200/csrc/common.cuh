@@ -71,13 +71,16 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 // The gated activation behind a feed-forward's first product, with its constants:
 // out = g' * sigmoid(alpha * g') * (u' + shift), g' = min(g, limit), u' = clamp(u, -limit, limit)
 // (limit 0: no clamp).  SwiGLU is {0, 1, 0}, for which the arithmetic below is the plain form's.
+// alpha == 0 selects the tanh form of gelu for the gate's factor instead, 0.5 g (1 + tanh(c (g + 0.044715 g^3)))
+// with c = sqrt(2 / pi), written as g * sigmoid(2 c (g + 0.044715 g^3)), which is the same function.
 struct GluForm { float limit, alpha, shift; };
 __device__ __forceinline__ float glu_apply(const GluForm f, float g, float u) {
     if (f.limit > 0.f) {
         g = fminf(g, f.limit);
         u = fminf(fmaxf(u, -f.limit), f.limit);
     }
-    return g / (1.0f + __expf(-f.alpha * g)) * (u + f.shift);
+    const float z = f.alpha == 0.f ? 1.5957691216057308f * (g + 0.044715f * g * g * g) : f.alpha * g;
+    return g / (1.0f + __expf(-z)) * (u + f.shift);
 }
 
 // Programmatic dependent launch (griddepcontrol): `pdl_wait` blocks until the kernels this one

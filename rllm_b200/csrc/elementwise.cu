@@ -37,6 +37,76 @@ RLLM_API int rllm_embed(const void* table, int table_dtype, const int* tokens, f
     return rllm_launch(embed_kernel<bf16>, dim3(n), dim3(threads), 0, stream, (const bf16*)table, tokens, out, d, vocab, err);
 }
 
+// Embedding with a scale and a second table looked up by the pair (previous token, token):
+//   out[t] = table[tok] * scale + pair_table[row],  row = (prev * mul_prev + tok * mul_cur) mod buckets,
+// and row = buckets (the table's last row) for a request's first token (position 0).  The previous
+// token is the row before in the step, or, for the first row a request brings, the id kept in
+// last_tok[slot] by the step before (keep_last_tokens below, a launch of its own so that no block
+// reads a slot that another one writes).  The product runs in 64 bits, so no sizes overflow.
+template <typename TW>
+__global__ void embed_pair_kernel(const TW* __restrict__ table, const TW* __restrict__ pair_table,
+                                  const int* __restrict__ tokens, const int* __restrict__ positions,
+                                  const int* __restrict__ seq_ids, const int* __restrict__ cu_q,
+                                  const int* __restrict__ slots, const int* last_tok, float* __restrict__ out,
+                                  int d, int vocab, float scale, int buckets, long long mul_prev, long long mul_cur,
+                                  int* err) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    int tok = tokens[t];
+    if (tok < 0 || tok >= vocab) {
+        if (threadIdx.x == 0 && err) atomicExch(err, RLLM_ERR_TOKEN);
+        tok = 0;
+    }
+    int row = buckets;
+    if (positions[t] > 0) {
+        const int r = seq_ids[t];
+        int prev = t > cu_q[r] ? tokens[t - 1] : last_tok[slots[r]];
+        if (prev < 0 || prev >= vocab) {
+            if (threadIdx.x == 0 && err) atomicExch(err, RLLM_ERR_TOKEN);
+            prev = 0;
+        }
+        row = (int)(((long long)prev * mul_prev + (long long)tok * mul_cur) % (long long)buckets);
+    }
+    const TW* src = table + (size_t)tok * d;
+    const TW* two = pair_table + (size_t)row * d;
+    float* dst = out + (size_t)t * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = to_f<TW>(src[i]) * scale + to_f<TW>(two[i]);
+}
+
+RLLM_API int rllm_embed_pair(const void* table, const void* pair_table, int table_dtype, const int* tokens,
+                             const int* positions, const int* seq_ids, const int* cu_q, const int* slots,
+                             const int* last_tok, float* out, int n, int d, int vocab, float scale, int buckets,
+                             long long mul_prev, long long mul_cur, int* err, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (buckets <= 0 || mul_prev < 0 || mul_cur < 0) return (int)cudaErrorInvalidValue;
+    const int threads = d >= 1024 ? 256 : 128;
+    if (table_dtype == RLLM_F32)
+        return rllm_launch(embed_pair_kernel<float>, dim3(n), dim3(threads), 0, stream, (const float*)table,
+                           (const float*)pair_table, tokens, positions, seq_ids, cu_q, slots, last_tok, out, d, vocab,
+                           scale, buckets, mul_prev, mul_cur, err);
+    return rllm_launch(embed_pair_kernel<bf16>, dim3(n), dim3(threads), 0, stream, (const bf16*)table,
+                       (const bf16*)pair_table, tokens, positions, seq_ids, cu_q, slots, last_tok, out, d, vocab, scale,
+                       buckets, mul_prev, mul_cur, err);
+}
+
+// last_tok[slots[r]] = the last token request r brings in this step (one thread per request).
+__global__ void keep_last_tokens_kernel(const int* __restrict__ tokens, const int* __restrict__ cu_q,
+                                        const int* __restrict__ slots, int* last_tok, int n_requests) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= n_requests) return;
+    const int e = cu_q[r + 1];
+    if (e > cu_q[r]) last_tok[slots[r]] = tokens[e - 1];
+}
+RLLM_API int rllm_keep_last_tokens(const int* tokens, const int* cu_q, const int* slots, int* last_tok,
+                                   int n_requests, cudaStream_t stream) {
+    if (n_requests <= 0) return 0;
+    return rllm_launch(keep_last_tokens_kernel, dim3((n_requests + 63) / 64), dim3(64), 0, stream, tokens, cu_q,
+                       slots, last_tok, n_requests);
+}
+
 // ------------------------------------------------------------------ add + RMSNorm
 // For output row r: src = rows ? rows[r] : r; v = x[src] (+ delta[src]);
 // if write_x the sum is stored back to x[src] (the residual stream);
@@ -402,6 +472,8 @@ RLLM_API int rllm_qk_norm_rope_store(const void* qkv, int in_dtype, const float*
 
 // the packed-argument forms (common.cuh) for the host runtime's replay of recorded launches
 RLLM_PACKED(rllm_embed)
+RLLM_PACKED(rllm_embed_pair)
+RLLM_PACKED(rllm_keep_last_tokens)
 RLLM_PACKED(rllm_add_rms_norm)
 RLLM_PACKED(rllm_add_inplace)
 RLLM_PACKED(rllm_silu_mul)

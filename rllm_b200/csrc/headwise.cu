@@ -18,8 +18,11 @@
 //                      values (heads of another size) into the paged cache; rows of queries only too.
 //   join_norm_rows     x += y / rms(y) * w_out and out = x / rms(x) * w_next in one pass: a norm on a
 //                      sublayer's output followed by the norm in front of the next sublayer.
+//   sum_norm_rows      x = (alpha * x + y) / rms(alpha * x + y) * w: the norm stands AFTER the residual sum
+//                      and the normed rows ARE the stream; low[t] = x in the activation type (optional).
 //   glu_clamped        out = g * sigmoid(alpha * g) * (u + shift), g = min(gate, limit),
-//                      u = clamp(up, -limit, limit).
+//                      u = clamp(up, -limit, limit); alpha 0: the tanh form of gelu in place of
+//                      g * sigmoid(alpha * g).
 //   softcap_rows       x = cap * tanh(x / cap) in place.
 //   masked_softmax_rows  a portion's score rows against its request's keys -> probabilities (causal,
 //                      optionally chunked and capped), for attention written as two library products.
@@ -209,7 +212,8 @@ RLLM_API int rllm_rope_unitnorm_store(const void* rows, int in_dt, long long ld,
 
 // ------------------------------------------------------------------ latent attention: cache row and query parts
 // One block per token.  kv[t] = [latent (rank) | shared key part (r)] with rows ld_kv apart (float32);
-// the latent is RMS-normed with a weight, the key part rotated (pairs (i, i + r/2)); both go to the
+// the latent is RMS-normed with a weight, the key part rotated (pairs (i, i + r/2), or (2i, 2i + 1) when
+// `pairs`); both go to the
 // token's cache row [rank + r] (one key/value head).  q[t] = H heads of [plain (dq) | rotated (r)]
 // with rows ld_q apart; the rotated part of head h goes to q_att[t, h, rank : rank + r] (the first
 // rank entries of each head are written by the product that takes the plain part into latent space).
@@ -218,7 +222,7 @@ __global__ void __launch_bounds__(256)
 latent_rope_store_kernel(const TQ* q, long long ld_q, const float* kv, long long ld_kv,
                          const float* __restrict__ kv_norm_w, const float2* cs_table, float cs_mult,
                          const int* __restrict__ slots, TO* q_att, TO* cache, int H, int dq, int r, int rank, int bs,
-                         float eps, int write_kv, int n_slots, int* err) {
+                         float eps, int write_kv, int n_slots, int* err, int pairs) {
     __shared__ float red[33];
     pdl_launch_dependents();
     pdl_wait();
@@ -231,10 +235,11 @@ latent_rope_store_kernel(const TQ* q, long long ld_q, const float* kv, long long
         const TQ* src = q + (size_t)t * ld_q + (size_t)h * (dq + r) + dq;
         const float2 a = cs[j];
         const float c = a.x * cs_mult, s = a.y * cs_mult;
-        const float u = to_f<TQ>(src[j]), w = to_f<TQ>(src[j + half]);
+        const int iu = pairs ? 2 * j : j, iv = pairs ? 2 * j + 1 : j + half;
+        const float u = to_f<TQ>(src[iu]), w = to_f<TQ>(src[iv]);
         TO* dst = q_att + ((size_t)t * H + h) * W + rank;
-        dst[j] = from_f<TO>(u * c - w * s);
-        dst[j + half] = from_f<TO>(w * c + u * s);
+        dst[iu] = from_f<TO>(u * c - w * s);
+        dst[iv] = from_f<TO>(w * c + u * s);
     }
     const float* row = kv + (size_t)t * ld_kv;
     float ss = 0.f;
@@ -253,16 +258,17 @@ latent_rope_store_kernel(const TQ* q, long long ld_q, const float* kv, long long
     for (int j = tid; j < half; j += blockDim.x) {
         const float2 a = cs[j];
         const float c = a.x * cs_mult, s = a.y * cs_mult;
-        const float u = row[rank + j], w = row[rank + j + half];
-        dst[rank + j] = from_f<TO>(u * c - w * s);
-        dst[rank + j + half] = from_f<TO>(w * c + u * s);
+        const int iu = pairs ? 2 * j : j, iv = pairs ? 2 * j + 1 : j + half;
+        const float u = row[rank + iu], w = row[rank + iv];
+        dst[rank + iu] = from_f<TO>(u * c - w * s);
+        dst[rank + iv] = from_f<TO>(w * c + u * s);
     }
 }
 
 RLLM_API int rllm_latent_rope_store(const void* q, int q_dt, long long ld_q, const float* kv, long long ld_kv,
                                     const float* kv_norm_w, const void* cs_table, float cs_mult, const int* slots,
                                     void* q_att, void* cache, int out_dt, int n, int H, int dq, int r, int rank,
-                                    int bs, float eps, int write_kv, long long n_slots, int* err,
+                                    int bs, float eps, int write_kv, long long n_slots, int* err, int pairs,
                                     cudaStream_t stream) {
     if (n <= 0) return 0;
     if (H <= 0 || dq <= 0 || r <= 0 || (r & 1) || rank <= 0 || bs <= 0 || !cs_table || !kv_norm_w ||
@@ -272,12 +278,47 @@ RLLM_API int rllm_latent_rope_store(const void* q, int q_dt, long long ld_q, con
 #define LAUNCH(TQ, TO)                                                                                           \
     return rllm_launch(latent_rope_store_kernel<TQ, TO>, dim3(n), dim3(256), 0, stream, (const TQ*)q, ld_q, kv,   \
                        ld_kv, kv_norm_w, (const float2*)cs_table, cs_mult, slots, (TO*)q_att, (TO*)cache, H, dq, r, \
-                       rank, bs, eps, write_kv, ns, err)
+                       rank, bs, eps, write_kv, ns, err, pairs)
     if (q_dt == RLLM_F32 && out_dt == RLLM_F32) { LAUNCH(float, float); }
     if (q_dt == RLLM_F32 && out_dt == RLLM_BF16) { LAUNCH(float, bf16); }
     if (q_dt == RLLM_BF16 && out_dt == RLLM_BF16) { LAUNCH(bf16, bf16); }
     return (int)cudaErrorInvalidValue;
 #undef LAUNCH
+}
+
+// ------------------------------------------------------------------ norm after the residual sum
+// One block per row: v = alpha * x[t] + y[t] (y in any type, rows ld_y apart), x[t] = v / rms(v) * w,
+// low[t] = the same in the activation type.  The sums are taken in float32 and the row is read twice
+// (it stays in L1/L2), so any width runs.
+__global__ void __launch_bounds__(256)
+sum_norm_rows_kernel(float* x, float alpha, const void* y, int y_dt, long long ld_y, const float* __restrict__ w,
+                     void* low, int low_dt, long long ld_low, int d, float eps) {
+    __shared__ float red[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t t = blockIdx.x;
+    float* xr = x + t * d;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float v = alpha * xr[i] + ld_dt(y, y_dt, t * ld_y + i);
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float rs = 1.0f / sqrtf(ss / (float)d + eps);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float v = (alpha * xr[i] + ld_dt(y, y_dt, t * ld_y + i)) * rs * w[i];
+        xr[i] = v;
+        if (low) st_dt(low, low_dt, t * ld_low + i, v);
+    }
+}
+
+RLLM_API int rllm_sum_norm_rows(float* x, float alpha, const void* y, int y_dt, long long ld_y, const float* w,
+                                void* low, int low_dt, long long ld_low, int n, int d, float eps,
+                                cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (d <= 0 || !x || !y || !w || ld_y < d || (low && ld_low < d)) return (int)cudaErrorInvalidValue;
+    return rllm_launch(sum_norm_rows_kernel, dim3(n), dim3(d >= 1024 ? 256 : 128), 0, stream, x, alpha, y, y_dt, ld_y,
+                       w, low, low_dt, ld_low, d, eps);
 }
 
 // ------------------------------------------------------------------ clamped gated activation
@@ -295,7 +336,9 @@ __global__ void glu_clamped_kernel(const void* gate_up, int in_dt, long long ld,
         g = fminf(g, limit);
         u = fminf(fmaxf(u, -limit), limit);
     }
-    st_dt(out, out_dt, i, g / (1.0f + expf(-alpha * g)) * (u + shift));
+    const float a = alpha == 0.f ? 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)))
+                                 : g / (1.0f + expf(-alpha * g));
+    st_dt(out, out_dt, i, a * (u + shift));
 }
 
 RLLM_API int rllm_glu_clamped(const void* gate_up, int in_dt, long long ld, void* out, int out_dt, int n, int F,
@@ -332,14 +375,18 @@ RLLM_API int rllm_softcap_rows(float* x, long long total, float cap, cudaStream_
 template <bool STAGED>
 __global__ void __launch_bounds__(256)
 masked_softmax_rows_kernel(const float* S, long long ld, bf16* P, long long ld_p, int H, int pos0, int n_cols,
-                           float scale, float softcap, int chunk) {
+                           float scale, float softcap, int chunk, int window, int col0) {
     extern __shared__ float staged[];
     __shared__ float red[33];
     pdl_wait();
     pdl_launch_dependents();
     const size_t row = blockIdx.x;
     const int pos = pos0 + (int)(row / H);
-    const int lo = chunk > 0 ? pos - pos % chunk : 0, hi = min(pos + 1, n_cols);
+    // column j holds the key at position col0 + j
+    int lo = chunk > 0 ? pos - pos % chunk : 0;
+    if (window > 0) lo = max(lo, pos + 1 - window);
+    lo = max(lo - col0, 0);
+    const int hi = min(pos + 1 - col0, n_cols);
     const float* s = S + row * ld;
     bf16* p = P + row * ld_p;
     float mx = -INFINITY;
@@ -380,15 +427,16 @@ masked_softmax_rows_kernel(const float* S, long long ld, bf16* P, long long ld_p
 }
 
 RLLM_API int rllm_masked_softmax_rows(const float* S, long long ld, void* P, long long ld_p, int rows, int H,
-                                      int pos0, int n_cols, float scale, float softcap, int chunk,
-                                      cudaStream_t stream) {
+                                      int pos0, int n_cols, float scale, float softcap, int chunk, int window,
+                                      int col0, cudaStream_t stream) {
     if (rows <= 0 || n_cols <= 0) return 0;
-    if (H <= 0 || pos0 < 0 || ld < n_cols || ld_p < n_cols || chunk < 0) return (int)cudaErrorInvalidValue;
+    if (H <= 0 || pos0 < 0 || ld < n_cols || ld_p < n_cols || chunk < 0 || window < 0 || col0 < 0)
+        return (int)cudaErrorInvalidValue;
     if (n_cols <= 11264)                     // 44 KB: within the shared memory every launch may have
         return rllm_launch(masked_softmax_rows_kernel<true>, dim3(rows), dim3(256), (size_t)n_cols * sizeof(float),
-                           stream, S, ld, (bf16*)P, ld_p, H, pos0, n_cols, scale, softcap, chunk);
+                           stream, S, ld, (bf16*)P, ld_p, H, pos0, n_cols, scale, softcap, chunk, window, col0);
     return rllm_launch(masked_softmax_rows_kernel<false>, dim3(rows), dim3(256), 0, stream, S, ld, (bf16*)P, ld_p, H,
-                       pos0, n_cols, scale, softcap, chunk);
+                       pos0, n_cols, scale, softcap, chunk, window, col0);
 }
 
 // ------------------------------------------------------------------ norm per head, then rotate, then store
@@ -624,4 +672,5 @@ RLLM_PACKED(rllm_norm_rows)
 RLLM_PACKED(rllm_rope_unitnorm_store)
 RLLM_PACKED(rllm_latent_rope_store)
 RLLM_PACKED(rllm_glu_clamped)
+RLLM_PACKED(rllm_sum_norm_rows)
 RLLM_PACKED(rllm_softcap_rows)

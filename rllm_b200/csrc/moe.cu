@@ -2,7 +2,7 @@
 // float32 arithmetic for everything the router does (accurate expf); products accumulate in float32 in a
 // fixed order, so a token's result does not depend on the batch around it.
 //
-//   moe_route        per token: scores from the router's logits (sigmoid, or softmax over all experts),
+//   moe_route        per token: scores from the router's logits (plus a stored bias per expert, if any; sigmoid, or softmax over all experts),
 //                    choice scores = scores + correction; experts form equal groups of neighbours, a
 //                    group's score is the sum of its `group_best` largest choice scores, only the
 //                    `keep_groups` best groups can be chosen from; the `top_k` largest choice scores win
@@ -25,7 +25,7 @@
 __global__ void __launch_bounds__(32)
 moe_route_kernel(const float* logits, long long ld, const float* __restrict__ correction, int* idx, float* weight,
                  int E, int top_k, int n_groups, int keep_groups, int group_best, int softmax, int normalize,
-                 float weight_eps, float route_scale) {
+                 float weight_eps, float route_scale, const float* __restrict__ bias) {
     __shared__ float s_score[MOE_MAX_EXPERTS];
     __shared__ float s_choice[MOE_MAX_EXPERTS];
     __shared__ float s_group[MOE_MAX_EXPERTS];
@@ -33,6 +33,11 @@ moe_route_kernel(const float* logits, long long ld, const float* __restrict__ co
     pdl_wait();
     const int t = blockIdx.x, lane = threadIdx.x;
     const float* z = logits + (size_t)t * ld;
+    if (bias) {                                              // the logits with their bias, staged in s_group
+        for (int e = lane; e < E; e += 32) s_group[e] = z[e] + bias[e];
+        __syncwarp();
+        z = s_group;
+    }
     if (softmax) {
         float m = -INFINITY;
         for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
@@ -50,7 +55,7 @@ moe_route_kernel(const float* logits, long long ld, const float* __restrict__ co
     }
     __syncwarp();
     for (int e = lane; e < E; e += 32) s_choice[e] = s_score[e] + (correction ? correction[e] : 0.f);
-    __syncwarp();
+    __syncwarp();                                            // (s_group is free again: z is not read below)
     const int per = E / n_groups;
     if (keep_groups < n_groups) {
         // a group's score: the sum of its largest choice scores (one lane per group, in index order)
@@ -120,13 +125,13 @@ moe_route_kernel(const float* logits, long long ld, const float* __restrict__ co
 
 RLLM_API int rllm_moe_route(const float* logits, long long ld, const float* correction, int* idx, float* weight, int n,
                             int E, int top_k, int n_groups, int keep_groups, int group_best, int softmax, int normalize,
-                            float weight_eps, float route_scale, cudaStream_t stream) {
+                            float weight_eps, float route_scale, const float* bias, cudaStream_t stream) {
     if (n <= 0) return 0;
     if (E <= 0 || E > MOE_MAX_EXPERTS || top_k <= 0 || top_k > E || n_groups <= 0 || E % n_groups || keep_groups <= 0 ||
         keep_groups > n_groups || group_best <= 0 || ld < E)
         return (int)cudaErrorInvalidValue;
     return rllm_launch(moe_route_kernel, dim3(n), dim3(32), 0, stream, logits, ld, correction, idx, weight, E, top_k,
-                       n_groups, keep_groups, group_best, softmax, normalize, weight_eps, route_scale);
+                       n_groups, keep_groups, group_best, softmax, normalize, weight_eps, route_scale, bias);
 }
 
 // ------------------------------------------------------------------ experts, pair by pair

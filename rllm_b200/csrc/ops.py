@@ -256,6 +256,30 @@ def embed(table, tokens, out, err=None):
     return out
 
 
+def embed_pair(table, pair_table, ctx_tokens, positions, seq_ids, cu_q, slots, last_tok, out, scale, buckets,
+               mul_prev, mul_cur, err=None):
+    """out[t] = table[token] * scale + pair_table[(previous * mul_prev + token * mul_cur) mod buckets], and
+    pair_table[buckets] for a request's first token; the previous token of the first row a request brings
+    is last_tok[slots[request]] (int32, written by keep_last_tokens after the step before)."""
+    _need_cuda(table, pair_table, ctx_tokens, positions, seq_ids, cu_q, slots, last_tok, out)
+    _need_contig(table=table, pair_table=pair_table, tokens=ctx_tokens, out=out, last_tok=last_tok)
+    n, d = out.shape
+    assert out.dtype == torch.float32 and table.shape[1] == d and pair_table.shape == (buckets + 1, d)
+    assert table.dtype == pair_table.dtype and last_tok.dtype == torch.int32
+    _check(core().rllm_embed_pair(_ptr(table), _ptr(pair_table), c_int(_code(table)), _ptr(ctx_tokens), _ptr(positions),
+                                  _ptr(seq_ids), _ptr(cu_q), _ptr(slots), _ptr(last_tok), _ptr(out), c_int(n), c_int(d),
+                                  c_int(table.shape[0]), c_float(scale), c_int(buckets), c_longlong(mul_prev),
+                                  c_longlong(mul_cur), _ptr(err), _stream()), "embed_pair")
+    return out
+
+
+def keep_last_tokens(ctx_tokens, cu_q, slots, last_tok, n_requests):
+    """last_tok[slots[r]] = the last token that request r brings in this step."""
+    _need_cuda(ctx_tokens, cu_q, slots, last_tok)
+    _check(core().rllm_keep_last_tokens(_ptr(ctx_tokens), _ptr(cu_q), _ptr(slots), _ptr(last_tok), c_int(n_requests),
+                                        _stream()), "keep_last_tokens")
+
+
 def add_rms_norm(x, delta, weight, out, eps, rows=None, write_x=True, delta_scale=1.0):
     """out[r] = rmsnorm(x[src] (+ delta_scale * delta[src])) * weight with src = rows[r] if rows is given
     else r.  x is the float32 residual stream and receives the sum when write_x (and delta is given)."""
@@ -397,6 +421,22 @@ def norm_rows(rows, weight, eps, x=None, add=False, low=None):
     return low if low is not None else x
 
 
+def sum_norm_rows(x, y, alpha, weight, eps, low=None):
+    """x = (alpha * x + y) / rms(alpha * x + y) * weight in place (x: the float32 stream, y: a sublayer's
+    output in any type); `low` (optional) takes the new rows in its own type."""
+    _need_cuda(x, y, weight, low)
+    _need_contig(x=x, weight=weight)
+    _rows2d(y, "y")
+    n, d = x.shape
+    assert x.dtype == torch.float32 and y.shape == (n, d) and weight.dtype == torch.float32 and weight.numel() == d
+    assert low is None or _rows2d(low, "low").shape == (n, d)
+    _check(core().rllm_sum_norm_rows(_ptr(x), c_float(alpha), _ptr(y), c_int(_code(y)), c_longlong(y.stride(0)),
+                                     _ptr(weight), _ptr(low), c_int(_code(low) if low is not None else F32),
+                                     c_longlong(low.stride(0) if low is not None else 0), c_int(n), c_int(d),
+                                     c_float(eps), _stream()), "sum_norm_rows")
+    return x
+
+
 def rope_unitnorm_store(rows, cs_table, rot, cs_mult, slots, q_out, k_cache, v_cache, H, G, hd, block_size, eps,
                         unit_norm=True, v_tied=True, write_kv=True):
     """rows [n, (H + G) * hd (+ G * hd values)] -> per head: the first `rot` entries rotated by the
@@ -467,10 +507,11 @@ def join_norm_rows(y, w_out, eps_out, x, w_next, eps_next, out):
 
 
 def latent_rope_store(q, kv, kv_norm_w, cs_table, cs_mult, slots, q_att, cache, H, dq, r, rank, block_size, eps,
-                      write_kv=True):
+                      write_kv=True, pairs=False):
     """Attention through latents, the step between the projections and the attention kernel: kv
     [n, rank + r] (float32, any row stride) -> cache row [normed latent | rotated shared key part];
-    q [n, H * (dq + r)] -> the rotated part of every head into q_att[:, h, rank:rank + r].  See headwise.cu."""
+    q [n, H * (dq + r)] -> the rotated part of every head into q_att[:, h, rank:rank + r].  `pairs`: entry 2i
+    turns with 2i + 1 (else i with i + r/2).  See headwise.cu."""
     _need_cuda(q, kv, kv_norm_w, cs_table, slots, q_att, cache)
     _need_contig(q_att=q_att, cache=cache, slots=slots)
     _rows2d(q, "q"), _rows2d(kv, "kv")
@@ -484,8 +525,12 @@ def latent_rope_store(q, kv, kv_norm_w, cs_table, cs_mult, slots, q_att, cache, 
         _ptr(q), c_int(_code(q)), c_longlong(q.stride(0)), _ptr(kv), c_longlong(kv.stride(0)), _ptr(kv_norm_w),
         _ptr(cs_table), c_float(cs_mult), _ptr(slots), _ptr(q_att), _ptr(cache), c_int(_code(q_att)), c_int(n),
         c_int(H), c_int(dq), c_int(r), c_int(rank), c_int(block_size), c_float(eps), c_int(1 if write_kv else 0),
-        c_longlong(cache.shape[0] * block_size), _ptr(error_word(q.device)), _stream()), "latent_rope_store")
+        c_longlong(cache.shape[0] * block_size), _ptr(error_word(q.device)), c_int(1 if pairs else 0), _stream()),
+        "latent_rope_store")
     return q_att
+
+
+GLU_GELU_TANH = (0.0, 0.0, 0.0)     # the `glu` triple (limit, alpha, shift) of act = tanh-form gelu: alpha 0 selects it
 
 
 def glu_clamped(gate_up, out, limit, alpha=1.0, shift=0.0):
@@ -523,19 +568,21 @@ def _rows2d(t, name):
     return t
 
 
-def rows_act(a, out, act=None, bias=None, mul=None, mul_act=None):
-    """out[t, c] = f(a[t, c] + bias[c]) * g(mul[t, c]); a, mul, out may be column slices of wider
-    matrices (any row stride), float32 or bfloat16; bias float32.  f, g by name (ACT)."""
+def rows_act(a, out, act=None, bias=None, mul=None, mul_act=None, mul_group=1):
+    """out[t, c] = f(a[t, c] + bias[c]) * g(mul[t, c // mul_group]); a, mul, out may be column slices of
+    wider matrices (any row stride), float32 or bfloat16; bias float32.  f, g by name (ACT).  mul_group > 1:
+    one factor for each run of that many columns (a gate per head)."""
     _need_cuda(a, out, bias, mul)
     _rows2d(a, "a"), _rows2d(out, "out")
     n, cols = out.shape
-    assert a.shape == (n, cols) and (mul is None or _rows2d(mul, "mul").shape == (n, cols))
+    assert mul_group >= 1 and cols % mul_group == 0
+    assert a.shape == (n, cols) and (mul is None or _rows2d(mul, "mul").shape == (n, cols // mul_group))
     assert bias is None or (bias.dtype == torch.float32 and bias.numel() == cols and bias.is_contiguous())
     _check(core().rllm_rows_act(_ptr(a), c_int(_code(a)), c_longlong(a.stride(0)), _ptr(bias), c_int(ACT[act]),
                                 _ptr(mul), c_int(_code(mul) if mul is not None else F32),
                                 c_longlong(mul.stride(0) if mul is not None else 0), c_int(ACT[mul_act]), _ptr(out),
-                                c_int(_code(out)), c_longlong(out.stride(0)), c_int(n), c_int(cols), _stream()),
-           "rows_act")
+                                c_int(_code(out)), c_longlong(out.stride(0)), c_int(n), c_int(cols), c_int(mul_group),
+                                _stream()), "rows_act")
     return out
 
 
@@ -563,10 +610,14 @@ def cat2_cast(x, y, out, delta=None, delta_scale=1.0):
 
 
 def qkv_rownorm_store(qkv, bias, q_norm_w, k_norm_w, slots, q_out, k_cache, v_cache, H, G, dk, dv, block_size, eps,
-                      write_kv=True):
+                      write_kv=True, cs_table=None, rot=0, pairs=False):
     """Biased q/k/v row -> RMSNorm over the whole q row and the whole k row (weights per column, None:
-    no norm) -> queries out, keys and values into the paged cache; see rowwise.cu."""
-    _need_cuda(qkv, bias, q_norm_w, k_norm_w, slots, q_out, k_cache, v_cache)
+    no norm) -> with `rot` > 0 the first rot entries of every query and key head rotated by the angles of
+    cs_table [n, rot/2, 2] (entry i with i + rot/2, or 2i with 2i + 1 when `pairs`) -> queries out, keys and
+    values into the paged cache; see rowwise.cu."""
+    _need_cuda(qkv, bias, q_norm_w, k_norm_w, slots, q_out, k_cache, v_cache, cs_table)
+    assert rot == 0 or (cs_table.dtype == torch.float32 and cs_table.shape == (qkv.shape[0], rot // 2, 2)
+                        and cs_table.is_contiguous() and rot % 2 == 0 and rot <= dk)
     _need_contig(q_out=q_out, k_cache=k_cache, v_cache=v_cache, slots=slots)
     _rows2d(qkv, "qkv")                       # may be the leading columns of a wider projection
     n = qkv.shape[0]
@@ -581,7 +632,8 @@ def qkv_rownorm_store(qkv, bias, q_norm_w, k_norm_w, slots, q_out, k_cache, v_ca
         _ptr(slots), _ptr(q_out),
         _ptr(k_cache), _ptr(v_cache), c_int(_code(q_out)), c_int(n), c_int(H), c_int(G), c_int(dk), c_int(dv),
         c_int(block_size), c_float(eps), c_int(1 if write_kv else 0), c_longlong(k_cache.shape[0] * block_size),
-        _ptr(error_word(qkv.device)), _stream()), "qkv_rownorm_store")
+        _ptr(error_word(qkv.device)), _ptr(cs_table if rot else None), c_int(rot), c_int(1 if pairs else 0), _stream()),
+        "qkv_rownorm_store")
     return q_out
 
 
@@ -797,13 +849,65 @@ def retention(rows, q_off, k_off, v_off, g_off, cs_table, rot, pairs, key_scale,
     return out
 
 
+def mlstm_state_floats(H: int, dk: int, dv: int) -> int:
+    """Floats of a request's matrix-memory state: per head the dk x (dv + 1) memory (the last column is the
+    normaliser) padded to the kernel's tile and in its threads' order, then four floats of which the first
+    is the running maximum (recurrent.cu).  No device needed."""
+    dkmax = 32 if dk <= 32 else 64 if dk <= 64 else 128 if dk <= 128 else 256
+    threads = ((dv + 2) // 2 * 8 + 31) // 32 * 32
+    return H * (dkmax * (threads // 8 * 2) + 4)
+
+
+def mlstm(rows, q_off, k_off, v_off, g_off, i_off, f_off, i_bias, f_bias, cap, q_scale, norm_w, eps, state, cu_q, slots,
+          out, n_requests, H, dk, dv, gate="sigmoid", segments=None):
+    """The matrix memory with exponential gates and a running maximum over each request's tokens, its
+    state in state[slot]; see recurrent.cu.  rows: float32 [n, ...] holding q, k ([H*dk] each), v, gate
+    ([H*dv] each) and the two gate pre-activations ([H] each) at the given column offsets; i_bias, f_bias
+    float32 [H]; norm_w float32 [H*dv] or None; out activation type [n, H*dv].  cap 0: the gates are not
+    capped."""
+    _need_cuda(rows, i_bias, f_bias, norm_w, state, cu_q, slots, out)
+    _rows2d(rows, "rows")
+    _need_contig(out=out)
+    n = out.shape[0]
+    assert rows.dtype == torch.float32 and rows.shape[0] == n and out.shape == (n, H * dv)
+    assert max(q_off, k_off) + H * dk <= rows.shape[1] and v_off + H * dv <= rows.shape[1]
+    assert max(i_off, f_off) + H <= rows.shape[1]
+    assert gate in (None, "none") or g_off + H * dv <= rows.shape[1]
+    for b in (i_bias, f_bias):
+        assert b is None or (b.dtype == torch.float32 and b.numel() == H and b.is_contiguous())
+    assert norm_w is None or (norm_w.dtype == torch.float32 and norm_w.numel() == H * dv and norm_w.is_contiguous())
+    if dk > 256 or dv > 254:
+        raise KernelError(f"head sizes {dk} x {dv} exceed the matrix-memory kernel's limits of 256 and 254")
+    st = _state2d(state)
+    per_head = mlstm_state_floats(1, dk, dv)
+    assert H * per_head <= st.shape[1]
+    sg = segments
+    carry = torch.empty((sg.n_items, H, per_head), dtype=torch.float32, device=out.device) if sg is not None else None
+    base = rows.data_ptr()
+    col = lambda off: c_void_p(base + 4 * off)
+    _ptr(rows)                                 # a traced launch keeps the rows alive
+    _check(_lib("recur").rllm_mlstm(
+        col(q_off), col(k_off), col(v_off), col(g_off) if GATES[gate] else c_void_p(0), col(i_off), col(f_off),
+        c_longlong(rows.stride(0)), _ptr(i_bias), _ptr(f_bias), c_float(cap), c_float(q_scale), _ptr(norm_w),
+        c_float(eps), _ptr(st), c_longlong(st.stride(0)), _ptr(cu_q), _ptr(slots), _ptr(out), c_int(_code(out)),
+        c_int(n_requests), c_int(H), c_int(dk), c_int(dv), c_int(GATES[gate]),
+        _ptr(sg.t0 if sg else None), _ptr(sg.t1 if sg else None), _ptr(sg.req if sg else None),
+        _ptr(sg.flags if sg else None), _ptr(sg.item0 if sg else None), _ptr(sg.items if sg else None),
+        c_int(sg.n_items if sg else 0), _ptr(carry), _stream()), "mlstm")
+    if sg is not None:
+        global _launches
+        _launches += 2                         # the local pass and the combine kernel
+    return out
+
+
 # ------------------------------------------------------------------ routed experts (moe.cu)
 
 def moe_route(logits, correction, idx, weight, E, top_k, n_groups=1, keep_groups=1, group_best=2, score="sigmoid",
-              normalize=True, weight_eps=0.0, route_scale=1.0):
-    """The router's choice per token from float32 logits (the first E columns of `logits`): idx int32
-    [n, top_k], weight float32 [n, top_k]; see moe.cu."""
-    _need_cuda(logits, correction, idx, weight)
+              normalize=True, weight_eps=0.0, route_scale=1.0, bias=None):
+    """The router's choice per token from float32 logits (the first E columns of `logits`, plus `bias`
+    float32 [E] if given): idx int32 [n, top_k], weight float32 [n, top_k]; see moe.cu."""
+    _need_cuda(logits, correction, idx, weight, bias)
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == E and bias.is_contiguous())
     _rows2d(logits, "logits")
     _need_contig(idx=idx, weight=weight, correction=correction)
     n = logits.shape[0]
@@ -817,7 +921,7 @@ def moe_route(logits, correction, idx, weight, E, top_k, n_groups=1, keep_groups
     _check(_lib("moe").rllm_moe_route(_ptr(logits), c_longlong(logits.stride(0)), _ptr(correction), _ptr(idx), _ptr(weight),
                                       c_int(n), c_int(E), c_int(top_k), c_int(n_groups), c_int(keep_groups),
                                       c_int(group_best), c_int(1 if score == "softmax" else 0), c_int(1 if normalize else 0),
-                                      c_float(weight_eps), c_float(route_scale), _stream()), "moe_route")
+                                      c_float(weight_eps), c_float(route_scale), _ptr(bias), _stream()), "moe_route")
     return idx, weight
 
 
@@ -1666,9 +1770,10 @@ def gemm_lib_nn(a, b, out):
     return out
 
 
-def masked_softmax_rows(scores, probs, H, pos0, n_cols, scale, softcap=0.0, chunk=0):
-    """scores [rows, >= n_cols] float32 (row = token * H + head, the token at position pos0 + token) ->
-    probs [rows, >= n_cols] bfloat16: softmax over the visible keys, zero elsewhere.  See headwise.cu."""
+def masked_softmax_rows(scores, probs, H, pos0, n_cols, scale, softcap=0.0, chunk=0, window=0, col0=0):
+    """scores [rows, >= n_cols] float32 (row = token * H + head, the token at position pos0 + token; column j
+    the key at position col0 + j) -> probs [rows, >= n_cols] bfloat16: softmax over the visible keys (causal;
+    inside the token's chunk; the last `window` keys), zero elsewhere.  See headwise.cu."""
     _need_cuda(scores, probs)
     _rows2d(scores, "scores"), _rows2d(probs, "probs")
     rows = scores.shape[0]
@@ -1676,7 +1781,8 @@ def masked_softmax_rows(scores, probs, H, pos0, n_cols, scale, softcap=0.0, chun
     assert scores.shape[1] >= n_cols and probs.shape[1] >= n_cols
     _check(core().rllm_masked_softmax_rows(_ptr(scores), c_longlong(scores.stride(0)), _ptr(probs),
                                            c_longlong(probs.stride(0)), c_int(rows), c_int(H), c_int(pos0),
-                                           c_int(n_cols), c_float(scale), c_float(softcap), c_int(chunk), _stream()),
+                                           c_int(n_cols), c_float(scale), c_float(softcap), c_int(chunk), c_int(window),
+                                           c_int(col0), _stream()),
            "masked_softmax_rows")
     return probs
 
@@ -1689,7 +1795,7 @@ def latent_decode_ok(q, hd, hdv) -> bool:
 
 
 def latent_decode_attention(q, cache, out, positions, seq_ids, block_table, H, hd, hdv, block_size, scale, softcap,
-                            max_ctx_len):
+                            max_ctx_len, window=0):
     """The decode shape of attention over one shared key/value head on the tensor cores (split keys,
     partials as scratch, merged by a second kernel); see attention_latent.cu."""
     _need_cuda(q, cache, out, positions, seq_ids, block_table)
@@ -1700,7 +1806,9 @@ def latent_decode_attention(q, cache, out, positions, seq_ids, block_table, H, h
     if not latent_decode_ok(q, hd, hdv):
         raise KernelError("latent_decode_attention takes bfloat16, key rows of a multiple of 16 entries up to 1152 and "
                           "values of a multiple of 64 entries up to 512")
-    n_splits = max(1, -(-int(max_ctx_len) // LATENT_SPLIT_KEYS))
+    # with a window the splits start at the window's first key rounded down to a tile of 32 keys
+    span = int(max_ctx_len) if window <= 0 else min(int(max_ctx_len), window + 31)
+    n_splits = max(1, -(-span // LATENT_SPLIT_KEYS))
     rows = n * (-(-H // 32)) * n_splits * 32
     part_o = torch.empty(rows * hdv, dtype=torch.float32, device=q.device)
     part_ml = torch.empty(rows * 2, dtype=torch.float32, device=q.device)
@@ -1708,13 +1816,13 @@ def latent_decode_attention(q, cache, out, positions, seq_ids, block_table, H, h
         _ptr(q), _ptr(cache), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(positions), _ptr(seq_ids), _ptr(block_table),
         c_int(block_table.stride(0)), c_int(n), c_int(H), c_int(hd), c_int(hdv), c_int(block_size), c_float(scale),
         c_float(softcap), c_int(LATENT_SPLIT_KEYS), c_int(n_splits), c_longlong(cache.shape[0]),
-        _ptr(error_word(q.device)), _stream()), "latent_decode_attention")
+        _ptr(error_word(q.device)), c_int(window), _stream()), "latent_decode_attention")
     global _launches
     _launches += 1                             # the merge kernel
     return out
 
 
-def shared_kv_attention(q, cache, out, ctx, block_table, H, hd, hdv, block_size, scale, softcap=0.0):
+def shared_kv_attention(q, cache, out, ctx, block_table, H, hd, hdv, block_size, scale, softcap=0.0, window=0):
     """Causal attention of H query heads over ONE key/value head whose values are the first hdv entries
     of the key rows (attention through a latent).  q [n, H * hd], cache [pages, 1, block_size, hd], out
     [n, H * hdv].  bfloat16 portions of more than DECODE_MAX_Q tokens are two library products around a
@@ -1722,7 +1830,8 @@ def shared_kv_attention(q, cache, out, ctx, block_table, H, hd, hdv, block_size,
     Q C^T for all its (token, head) rows at once (the heads share C, so the product has H times the rows
     of a head's own), probabilities, then P C[:, :hdv].  The other rows (decode steps, short portions)
     take the tensor-core decode kernel of attention_latent.cu where the sizes allow it; float32 and odd
-    sizes take the plain kernel."""
+    sizes take the plain kernel.  window > 0: a token sees its last `window` keys only (itself included);
+    the products then start at the page that holds the first visible key of a block of tokens."""
     n = q.shape[0]
     runs = []            # (first row, rows) of the tokens that take the plain kernel, merged
     big = []
@@ -1741,27 +1850,33 @@ def shared_kv_attention(q, cache, out, ctx, block_table, H, hd, hdv, block_size,
     for a, k in runs:
         if latent_decode_ok(q, hd, hdv):
             latent_decode_attention(q[a:a + k], cache, out[a:a + k], ctx.positions[a:a + k], ctx.seq_ids[a:a + k],
-                                    block_table, H, hd, hdv, block_size, scale, softcap, ctx.max_ctx_len)
+                                    block_table, H, hd, hdv, block_size, scale, softcap, ctx.max_ctx_len, window)
         else:
             paged_attention_generic(q[a:a + k], cache, cache, out[a:a + k], ctx.positions[a:a + k],
-                                    ctx.seq_ids[a:a + k], block_table, H, 1, hd, block_size, scale, 0, 0, hdv, 0, softcap)
+                                    ctx.seq_ids[a:a + k], block_table, H, 1, hd, block_size, scale, window, 0, hdv, 0,
+                                    softcap)
     for r, a, k in big:
         start, length = ctx.start_pos[r], ctx.start_pos[r] + k
         n_pages = -(-length // block_size)
-        keys = cache.index_select(0, block_table[r, :n_pages].long()).view(n_pages * block_size, hd)
-        L = n_pages * block_size
+        # with a window only the pages from the first visible key of the portion's first token on are read
+        # (earlier ones may have gone back to the pool)
+        page0 = max(0, start + 1 - window) // block_size if window > 0 else 0
+        first = page0 * block_size
+        keys = cache.index_select(0, block_table[r, page0:n_pages].long()).view((n_pages - page0) * block_size, hd)
+        L = (n_pages - page0) * block_size
         # blocks of tokens: a block's products stop at its last token's key, so shorter blocks skip more of the
         # masked upper triangle (a third of the work at four blocks) for three more launches each
         step = max(1, min(k, PRODUCTS_BLOCK_TOKENS, PRODUCTS_MAX_SCORE_BYTES // (4 * H * L)))
         for t0 in range(0, k, step):
             t1 = min(k, t0 + step)
             rows = (t1 - t0) * H
-            hi = min(L, -(-(start + t1) // 8) * 8)                # keys beyond the last token of these rows are not needed
-            scores = torch.empty((rows, hi), dtype=torch.float32, device=q.device)
-            gemm_lib(q[a + t0:a + t1].view(rows, hd), keys[:hi], scores)
-            probs = torch.empty((rows, hi), dtype=torch.bfloat16, device=q.device)
-            masked_softmax_rows(scores, probs, H, start + t0, hi, scale, softcap)
-            gemm_lib_nn(probs, keys[:hi, :hdv], out[a + t0:a + t1].view(rows, hdv))
+            hi = min(L, -(-(start + t1 - first) // 8) * 8)        # keys beyond the last token of these rows are not needed
+            lo = (max(0, start + t0 + 1 - window) - first) // 8 * 8 if window > 0 else 0    # nor those before the block's window
+            scores = torch.empty((rows, hi - lo), dtype=torch.float32, device=q.device)
+            gemm_lib(q[a + t0:a + t1].view(rows, hd), keys[lo:hi], scores)
+            probs = torch.empty((rows, hi - lo), dtype=torch.bfloat16, device=q.device)
+            masked_softmax_rows(scores, probs, H, start + t0, hi - lo, scale, softcap, window=window, col0=first + lo)
+            gemm_lib_nn(probs, keys[lo:hi, :hdv], out[a + t0:a + t1].view(rows, hdv))
     return out
 
 

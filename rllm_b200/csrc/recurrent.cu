@@ -1,6 +1,7 @@
 // Layers that carry a fixed-size state per request from token to token: the selective scan
 // (Mamba) with its short causal convolution, RWKV-style time mixing with a data-dependent
-// decay, and retention (linear attention with a fixed decay per head).  A request's state lives in a slot of the state array (float32), is read at the start of
+// decay, retention (linear attention with a fixed decay per head) and the matrix memory with
+// exponential gates and a running maximum (mLSTM).  A request's state lives in a slot of the state array (float32), is read at the start of
 // the request's tokens in this step and written back at their end; the tokens of a request are
 // contiguous in the flat batch (cu_q) and in order.  Everything that enters a recurrence (step
 // sizes, decays, their exponentials, gates, unit norms, the state itself) is float32 with accurate
@@ -15,6 +16,8 @@
 //           that a step reads and writes it in whole lines: value (register, thread) at register *
 //           threads + thread; then the previous token's input [width].  Nothing else reads S.
 //   retention:  S of every head, DKMAX * dvp floats a head, in the retention kernel's thread order.
+//   mlstm:  per head DKMAX * dvp floats in the same order, whose value column dv is the normaliser n, then
+//           four floats of which the first is the running maximum m.
 #include "common.cuh"
 #include <math.h>
 
@@ -967,7 +970,313 @@ RLLM_API long long rllm_retention_state_floats(int H, int dk, int dv) {
     return (long long)H * ret_dkmax(dk) * (ret_threads(dv) / RET_PARTS * 2);
 }
 
+// ------------------------------------------------------------------ matrix memory with exponential gates (mLSTM)
+// One block per (head, request or segment).  Per token, with q, k the head's rows (dk entries), v its
+// values (dv entries), and the head's two gate pre-activations x_i, x_f (a bias added here):
+//   i = cap * tanh(x_i / cap),  f = logsigmoid(cap * tanh(x_f / cap))            (cap 0: i = x_i, f = logsigmoid(x_f))
+//   m' = max(f + m, i);  a = exp(f + m - m'),  b = exp(i - m')
+//   S[e][j] = a * S[e][j] + b * k[e] * v[j];   n[e] = a * n[e] + b * k[e]
+//   o[j] = q_scale * sum_e q[e] S[e][j] / (max(|q_scale * n . q|, exp(-m')) + 1e-6)
+// then o is divided by its root mean square over the head (eps inside the root), multiplied by a weight
+// per column and by the gate's activation, and stored in the activation type.  m starts at 0 with S and n
+// (a zeroed slot).  The normaliser is carried as one more value column whose "value" is 1 for every
+// token, so the thread layout, the chunks of RET_TOK tokens and the slot order are the retention kernel's
+// with dv + 1 columns.  The chain of maxima is walked by one thread per chunk (two dependent operations a
+// token); the exponentials are then taken by one lane per token.
+// Cut along time (TimeSegments): pass 1 runs a segment from an empty memory with m = -infinity and keeps
+// (S, n, m) and the sum F of its f; with C = exp(m) S the true memory, C_end = exp(F) C_start + C_local
+// and m_end = max(F + m_start, m_local), so   S_end = exp(F + m_start - m_end) S_start + exp(m_local -
+// m_end) S_local   (mlstm_combine); pass 2 runs every segment from its true start and writes outputs.
+// Scalars behind a head's S, in the slot and in a carry: [0] m, [1] F (carry), [2] m_local (carry).
+#define MLSTM_SCALARS 4
+
+template <typename TA, int DKMAX, int PASS, int MAXT>
+__global__ void __launch_bounds__(MAXT)
+mlstm_kernel(const float* qp, const float* kp, const float* vp, const float* gp, const float* ip, const float* fp,
+             long long ld, const float* __restrict__ i_bias, const float* __restrict__ f_bias, float cap, float q_scale,
+             const float* __restrict__ norm_w, float eps, float* state, long long slot_stride,
+             const int* __restrict__ cu_q, const int* __restrict__ slots, TA* out, int H, int dk, int dv, int gate,
+             const TimeSegments seg) {
+    constexpr int IPT = DKMAX / RET_PARTS;
+    extern __shared__ __align__(16) float sm_ml[];
+    const int NT = blockDim.x, dvp = NT / RET_PARTS * 2;
+    const int stage = RET_TOK * (2 * DKMAX + 2 * dvp + 2);
+    float* s_o = sm_ml + 2 * stage;                       // [RET_TOK][dvp]
+    float* s_a = s_o + RET_TOK * dvp;                     // a, b, exp(-m'), m' per token of the chunk
+    float* s_b = s_a + RET_TOK;
+    float* s_em = s_b + RET_TOK;
+    float* s_m = s_em + RET_TOK;                          // [RET_TOK + 1]: m before the chunk, then after each token
+    const int tid = threadIdx.x, j0 = 2 * (tid / RET_PARTS), part = tid % RET_PARTS;
+    const int head = blockIdx.x, item = blockIdx.y;
+    pdl_wait();
+    pdl_launch_dependents();
+    const int r = PASS == 0 ? item : seg.req[item];
+    const int t0 = PASS == 0 ? cu_q[r] : seg.t0[item], t1 = PASS == 0 ? cu_q[r + 1] : seg.t1[item];
+    const bool first = PASS == 0 || (seg.flags[item] & 1), last = PASS == 0 || (seg.flags[item] & 2);
+    if (PASS == 1 && last) return;                        // its end state comes out of pass 2
+    const size_t per_S = (size_t)DKMAX * dvp, per_head = per_S + MLSTM_SCALARS;
+    float* Sg = state + (size_t)slots[r] * slot_stride + (size_t)head * per_head;
+    float S0[IPT], S1[IPT];
+    float m_run, f_sum = 0.f;                             // thread 0's: the running maximum, the sum of f
+    {
+        const int src = first ? item + seg.req_items[r] - 1 : item - 1;
+        const float* from = (first && last) ? Sg : seg.carry + ((size_t)src * H + head) * per_head;
+#pragma unroll
+        for (int ii = 0; ii < IPT; ++ii) {
+            S0[ii] = PASS == 1 ? 0.f : from[(size_t)(2 * ii) * NT + tid];
+            S1[ii] = PASS == 1 ? 0.f : from[(size_t)(2 * ii + 1) * NT + tid];
+        }
+        m_run = PASS == 1 ? -INFINITY : from[per_S];
+    }
+    const size_t qcol = (size_t)head * dk, vcol = (size_t)head * dv;
+    const float ib = i_bias ? i_bias[head] : 0.f, fb = f_bias ? f_bias[head] : 0.f;
+    auto issue = [&](int tb, int buf) {
+        float* base = sm_ml + buf * stage;
+        const int nt = min(RET_TOK, t1 - tb);
+        for (int e = tid; e < 2 * RET_TOK * DKMAX; e += NT) {
+            const int arr = e / (RET_TOK * DKMAX), rem = e % (RET_TOK * DKMAX), tt = rem / DKMAX, cc = rem % DKMAX;
+            if (tt < nt && cc < dk) ret_cp_async4(base + e, (arr ? kp : qp) + (size_t)(tb + tt) * ld + qcol + cc);
+            else base[e] = 0.f;
+        }
+        float* vb = base + 2 * RET_TOK * DKMAX;
+        for (int e = tid; e < 2 * RET_TOK * dvp; e += NT) {
+            const int arr = e / (RET_TOK * dvp), rem = e % (RET_TOK * dvp), tt = rem / dvp, cc = rem % dvp;
+            if (tt < nt && cc < dv && (arr == 0 || gp)) ret_cp_async4(vb + e, (arr ? gp : vp) + (size_t)(tb + tt) * ld + vcol + cc);
+            else vb[e] = (arr == 0 && tt < nt && cc == dv) ? 1.f : 0.f;          // the normaliser's column
+        }
+        float* gb = vb + 2 * RET_TOK * dvp;                                     // the gates' pre-activations
+        for (int e = tid; e < 2 * RET_TOK; e += NT) {
+            const int arr = e / RET_TOK, tt = e % RET_TOK;
+            if (tt < nt) ret_cp_async4(gb + e, (arr ? fp : ip) + (size_t)(tb + tt) * ld + head);
+            else gb[e] = 0.f;
+        }
+        asm volatile("cp.async.commit_group;\n" ::);
+    };
+    const int warp = tid >> 5, lane = tid & 31, n_warps = NT >> 5;
+    if (t0 < t1) issue(t0, 0);
+    int buf = 0;
+    for (int tb = t0; tb < t1; tb += RET_TOK, buf ^= 1) {
+        const int nt = min(RET_TOK, t1 - tb);
+        const bool more = tb + RET_TOK < t1;
+        if (more) {
+            issue(tb + RET_TOK, buf ^ 1);
+            asm volatile("cp.async.wait_group 1;\n" ::);
+        } else {
+            asm volatile("cp.async.wait_group 0;\n" ::);
+        }
+        __syncthreads();
+        float* s_q = sm_ml + buf * stage;
+        float* s_k = s_q + RET_TOK * DKMAX;
+        float* s_v = s_k + RET_TOK * DKMAX;
+        float* s_g = s_v + RET_TOK * dvp;
+        float* s_ig = s_g + RET_TOK * dvp;
+        float* s_fg = s_ig + RET_TOK;
+        // the gates: one lane per token, then the chain of maxima by one thread, then the exponentials
+        if (tid < nt) {
+            const float xi = s_ig[tid] + ib, xf = s_fg[tid] + fb;
+            s_ig[tid] = cap > 0.f ? cap * tanhf(xi / cap) : xi;
+            s_fg[tid] = -softplus_f(-(cap > 0.f ? cap * tanhf(xf / cap) : xf));
+        }
+        __syncthreads();
+        if (tid == 0) {
+            s_m[0] = m_run;
+            for (int tt = 0; tt < nt; ++tt) {
+                m_run = fmaxf(s_fg[tt] + m_run, s_ig[tt]);
+                s_m[tt + 1] = m_run;
+                f_sum += s_fg[tt];
+            }
+        }
+        __syncthreads();
+        if (tid < nt) {
+            const float mo = s_m[tid], mn = s_m[tid + 1];
+            s_a[tid] = mo == -INFINITY ? 0.f : expf(s_fg[tid] + mo - mn);
+            s_b[tid] = expf(s_ig[tid] - mn);
+            s_em[tid] = expf(-mn);
+        }
+        __syncthreads();
+        auto token = [&](int tt) {
+            const float a = s_a[tt], b = s_b[tt];
+            float2 vj = *reinterpret_cast<const float2*>(s_v + tt * dvp + j0);
+            vj.x *= b;
+            vj.y *= b;
+            const float4* q4 = reinterpret_cast<const float4*>(s_q + tt * DKMAX);
+            const float4* k4 = reinterpret_cast<const float4*>(s_k + tt * DKMAX);
+            float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+#pragma unroll
+            for (int q = 0; q < IPT / 4; ++q) {
+                const float4 qq = q4[part + RET_PARTS * q], kk = k4[part + RET_PARTS * q];
+#define ML_STEP(Q, K, I, A, B)                                                   \
+                S0[I] = a * S0[I] + K * vj.x; S1[I] = a * S1[I] + K * vj.y;      \
+                if (PASS != 1) { A += Q * S0[I]; B += Q * S1[I]; }
+                ML_STEP(qq.x, kk.x, 4 * q, a0, b0)
+                ML_STEP(qq.y, kk.y, 4 * q + 1, a1, b1)
+                ML_STEP(qq.z, kk.z, 4 * q + 2, a0, b0)
+                ML_STEP(qq.w, kk.w, 4 * q + 3, a1, b1)
+#undef ML_STEP
+            }
+            if (PASS == 1) return;
+            float oa = a0 + a1, ob = b0 + b1;
+#pragma unroll
+            for (int m = 1; m < RET_PARTS; m <<= 1) {
+                oa += __shfl_xor_sync(0xffffffffu, oa, m);
+                ob += __shfl_xor_sync(0xffffffffu, ob, m);
+            }
+            if (part == 0) *reinterpret_cast<float2*>(s_o + tt * dvp + j0) = make_float2(oa, ob);
+        };
+        if (nt == RET_TOK) {
+#pragma unroll 2
+            for (int tt = 0; tt < RET_TOK; ++tt) token(tt);
+        } else {
+            for (int tt = 0; tt < nt; ++tt) token(tt);
+        }
+        __syncthreads();
+        for (int tt = warp; PASS != 1 && tt < nt; tt += n_warps) {
+            const float nq = s_o[tt * dvp + dv] * q_scale;
+            const float inv = q_scale / (fmaxf(fabsf(nq), s_em[tt]) + 1e-6f);
+            float ss = 0.f;
+            for (int i = lane; i < dv; i += 32) {
+                const float o = s_o[tt * dvp + i] * inv;
+                ss += o * o;
+            }
+            const float rs = 1.0f / sqrtf(warp_sum(ss) / (float)dv + eps);
+            for (int i = lane; i < dv; i += 32) {
+                float v = s_o[tt * dvp + i] * inv * rs;
+                if (norm_w) v *= norm_w[vcol + i];
+                if (gate == 1) v *= silu_f(s_g[tt * dvp + i]);
+                else if (gate == 2) v *= 1.0f / (1.0f + expf(-s_g[tt * dvp + i]));
+                out[(size_t)(tb + tt) * H * dv + vcol + i] = from_f<TA>(v);
+            }
+        }
+        __syncthreads();                                  // everyone is done with this buffer, s_o and the gates
+    }
+    float* to = PASS == 1 ? seg.carry + ((size_t)item * H + head) * per_head : Sg;
+    if (PASS != 1 && !last) return;
+#pragma unroll
+    for (int ii = 0; ii < IPT; ++ii) {
+        to[(size_t)(2 * ii) * NT + tid] = S0[ii];
+        to[(size_t)(2 * ii + 1) * NT + tid] = S1[ii];
+    }
+    if (tid == 0) {
+        if (PASS == 1) { to[per_S + 1] = f_sum; to[per_S + 2] = m_run; }
+        else to[per_S] = m_run;
+    }
+}
+
+// Between the passes: a request's segments in order, in place; a thread carries one entry of S (or of n).
+__global__ void __launch_bounds__(RET_COMBINE_THREADS)
+mlstm_combine_kernel(const float* state, long long slot_stride, const int* __restrict__ slots, int H, int per_S,
+                     const TimeSegments seg) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int head = blockIdx.x, r = blockIdx.y;
+    const int i = blockIdx.z * RET_COMBINE_THREADS + threadIdx.x;
+    const int n = seg.req_items[r], item0 = seg.req_item0[r];
+    if (n < 2 || i >= per_S) return;
+    const size_t per_head = (size_t)per_S + MLSTM_SCALARS;
+    const float* from = state + (size_t)slots[r] * slot_stride + (size_t)head * per_head;
+    float S = from[i], m = from[per_S];
+    float* start = seg.carry + ((size_t)(item0 + n - 1) * H + head) * per_head;   // the start state, for pass 2
+    start[i] = S;
+    if (i == 0) start[per_S] = m;
+    for (int it = item0; it < item0 + n - 1; ++it) {
+        float* C = seg.carry + ((size_t)it * H + head) * per_head;
+        const float F = C[per_S + 1], ml = C[per_S + 2];
+        const float mn = fmaxf(F + m, ml);
+        S = expf(F + m - mn) * S + expf(ml - mn) * C[i];
+        m = mn;
+        C[i] = S;
+        if (i == 0) C[per_S] = m;
+    }
+}
+
+static inline int mlstm_threads(int dv) { return ret_threads(dv + 1); }
+
+template <typename TA, int DKMAX, int PASS, int MAXT>
+static int launch_mlstm_pass(dim3 grid, int threads, size_t smem, cudaStream_t stream, const float* qp, const float* kp,
+                             const float* vp, const float* gp, const float* ip, const float* fp, long long ld,
+                             const float* i_bias, const float* f_bias, float cap, float q_scale, const float* norm_w,
+                             float eps, float* state, long long slot_stride, const int* cu_q, const int* slots, void* out,
+                             int H, int dk, int dv, int gate, const TimeSegments& seg) {
+    if (smem > 48 * 1024) {
+        static size_t raised = 0;
+        if (smem > raised) {
+            cudaError_t e = cudaFuncSetAttribute(mlstm_kernel<TA, DKMAX, PASS, MAXT>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+            raised = smem;
+        }
+    }
+    return rllm_launch(mlstm_kernel<TA, DKMAX, PASS, MAXT>, grid, dim3(threads), smem, stream, qp, kp, vp, gp, ip, fp, ld,
+                       i_bias, f_bias, cap, q_scale, norm_w, eps, state, slot_stride, cu_q, slots, (TA*)out, H, dk, dv,
+                       gate, seg);
+}
+
+template <typename TA, int DKMAX, int MAXT>
+static int launch_mlstm(int n_requests, int threads, size_t smem, cudaStream_t stream, const float* qp, const float* kp,
+                        const float* vp, const float* gp, const float* ip, const float* fp, long long ld,
+                        const float* i_bias, const float* f_bias, float cap, float q_scale, const float* norm_w, float eps,
+                        float* state, long long slot_stride, const int* cu_q, const int* slots, void* out, int H, int dk,
+                        int dv, int gate, const TimeSegments& seg) {
+#define ML_ARGS qp, kp, vp, gp, ip, fp, ld, i_bias, f_bias, cap, q_scale, norm_w, eps, state, slot_stride, cu_q, slots, out, H, dk, dv, gate, seg
+    if (seg.n_items <= 0)
+        return launch_mlstm_pass<TA, DKMAX, 0, MAXT>(dim3(H, n_requests), threads, smem, stream, ML_ARGS);
+    int st = launch_mlstm_pass<TA, DKMAX, 1, MAXT>(dim3(H, seg.n_items), threads, smem, stream, ML_ARGS);
+    if (st) return st;
+    const int per_S = DKMAX * (threads / RET_PARTS * 2);
+    st = rllm_launch(mlstm_combine_kernel, dim3(H, n_requests, (per_S + RET_COMBINE_THREADS - 1) / RET_COMBINE_THREADS),
+                     dim3(RET_COMBINE_THREADS), 0, stream, (const float*)state, slot_stride, slots, H, per_S, seg);
+    if (st) return st;
+    return launch_mlstm_pass<TA, DKMAX, 2, MAXT>(dim3(H, seg.n_items), threads, smem, stream, ML_ARGS);
+#undef ML_ARGS
+}
+
+// q, k [n, H*dk], v, gate [n, H*dv], the gates' pre-activations ip, fp [n, H]: float32 columns of one
+// projection (rows ld apart); i_bias, f_bias [H] or null; norm_w [H*dv] or null; gate_kind 0: none, 1: silu,
+// 2: sigmoid.  carry needs n_items * H * (DKMAX * dvp + 4) floats.
+RLLM_API int rllm_mlstm(const float* qp, const float* kp, const float* vp, const float* gp, const float* ip,
+                        const float* fp, long long ld, const float* i_bias, const float* f_bias, float cap, float q_scale,
+                        const float* norm_w, float eps, float* state, long long slot_stride, const int* cu_q,
+                        const int* slots, void* out, int act_dt, int n_requests, int H, int dk, int dv, int gate_kind,
+                        const int* seg_t0, const int* seg_t1, const int* seg_req, const int* seg_flags,
+                        const int* req_item0, const int* req_items, int n_items, float* carry, cudaStream_t stream) {
+    if (n_requests <= 0) return 0;
+    if (dk <= 0 || dk > 256 || dv <= 0 || dv > 254 || H <= 0 || cap < 0.f || (gate_kind && !gp) || !ip || !fp)
+        return (int)cudaErrorInvalidValue;
+    const int dkmax = ret_dkmax(dk), threads = mlstm_threads(dv), dvp = threads / RET_PARTS * 2;
+    TimeSegments seg = {seg_t0, seg_t1, seg_req, seg_flags, req_item0, req_items, carry, nullptr, n_items};
+    if (n_items > 0 && (!seg_t0 || !seg_t1 || !seg_req || !seg_flags || !req_item0 || !req_items || !carry))
+        return (int)cudaErrorInvalidValue;
+    const size_t smem = ((size_t)2 * RET_TOK * (2 * dkmax + 2 * dvp + 2) + (size_t)RET_TOK * dvp + 4 * RET_TOK + 4) * sizeof(float);
+#define LAUNCH(TA, DKMAX, MAXT)                                                                                    \
+    return launch_mlstm<TA, DKMAX, MAXT>(n_requests, threads, smem, stream, qp, kp, vp, gp, ip, fp, ld, i_bias, f_bias, \
+                                         cap, q_scale, norm_w, eps, state, slot_stride, cu_q, slots, out, H, dk, dv, \
+                                         gate_kind, seg)
+#define BY_D(TA)                                                                                               \
+    do {                                                                                                       \
+        if (threads > 512) {                                                                                   \
+            if (dkmax == 32) { LAUNCH(TA, 32, 1024); }                                                         \
+            if (dkmax == 64) { LAUNCH(TA, 64, 1024); }                                                         \
+            if (dkmax == 128) { LAUNCH(TA, 128, 1024); }                                                       \
+            LAUNCH(TA, 256, 1024);                                                                             \
+        }                                                                                                      \
+        if (dkmax == 32) { LAUNCH(TA, 32, 512); }                                                              \
+        if (dkmax == 64) { LAUNCH(TA, 64, 512); }                                                              \
+        if (dkmax == 128) { LAUNCH(TA, 128, 512); }                                                            \
+        LAUNCH(TA, 256, 512);                                                                                  \
+    } while (0)
+    if (act_dt == RLLM_F32) BY_D(float);
+    BY_D(bf16);
+#undef BY_D
+#undef LAUNCH
+}
+
+// Floats of a request's mLSTM state for H heads of dk x dv (no device needed).
+RLLM_API long long rllm_mlstm_state_floats(int H, int dk, int dv) {
+    return (long long)H * ((long long)ret_dkmax(dk) * (mlstm_threads(dv) / RET_PARTS * 2) + MLSTM_SCALARS);
+}
+
 RLLM_PACKED(rllm_conv_silu)
+RLLM_PACKED(rllm_mlstm)
 RLLM_PACKED(rllm_retention)
 RLLM_PACKED(rllm_selective_scan)
 RLLM_PACKED(rllm_token_shift)

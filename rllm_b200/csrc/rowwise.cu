@@ -1,12 +1,14 @@
 // Row-wise helpers that several kinds of layers share; float32 arithmetic whatever the storage
 // type, accurate expf / tanhf / log1pf (no fast-math):
 //
-//   rows_act        out[t, c] = f1(in[t, c] + bias[c]) * f2(mul[t, c])       (bias, mul optional)
+//   rows_act        out[t, c] = f1(in[t, c] + bias[c]) * f2(mul[t, c / mul_group])   (bias, mul optional;
+//                   mul_group > 1: one factor for each run of that many columns, a gate per head)
 //   axpby           out = a * x + b * y                                      (float32)
 //   cat2_cast       out[t] = [x[t] + s * delta[t] | y[t]] in the activation type (delta optional)
 //   qkv_rownorm_store  biased q/k/v projection row -> RMSNorm over the WHOLE q row and the whole k
-//                   row (one weight per column), queries out, keys and values into the paged cache;
-//                   the value heads may have another size than the key heads
+//                   row (one weight per column), then optionally the rotation of the first `rot` entries
+//                   of every query and key head by the step's angles; queries out, keys and values into
+//                   the paged cache; the value heads may have another size than the key heads
 //
 // f1, f2: 0 identity, 1 silu z / (1 + e^-z), 2 relu(z)^2, 3 sigmoid, 4 tanh, 5 softplus.
 #include "common.cuh"
@@ -34,7 +36,7 @@ __device__ __forceinline__ void st_any(void* p, int dt, size_t i, float v) {
 
 __global__ void rows_act_kernel(const void* in, int in_dt, long long in_stride, const float* __restrict__ bias,
                                 int act1, const void* mul, int mul_dt, long long mul_stride, int act2, void* out,
-                                int out_dt, long long out_stride, int cols, size_t total) {
+                                int out_dt, long long out_stride, int cols, size_t total, int mul_group) {
     pdl_wait();
     pdl_launch_dependents();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -44,17 +46,19 @@ __global__ void rows_act_kernel(const void* in, int in_dt, long long in_stride, 
     float v = ld_any(in, in_dt, t * in_stride + c);
     if (bias) v += bias[c];
     v = act_apply(v, act1);
-    if (mul) v *= act_apply(ld_any(mul, mul_dt, t * mul_stride + c), act2);
+    if (mul) v *= act_apply(ld_any(mul, mul_dt, t * mul_stride + c / mul_group), act2);
     st_any(out, out_dt, t * out_stride + c, v);
 }
 
 RLLM_API int rllm_rows_act(const void* in, int in_dt, long long in_stride, const float* bias, int act1,
                            const void* mul, int mul_dt, long long mul_stride, int act2, void* out, int out_dt,
-                           long long out_stride, int n, int cols, cudaStream_t stream) {
+                           long long out_stride, int n, int cols, int mul_group, cudaStream_t stream) {
     const size_t total = (size_t)n * cols;
     if (total == 0) return 0;
+    if (mul_group <= 0) return (int)cudaErrorInvalidValue;
     return rllm_launch(rows_act_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, in, in_dt,
-                       in_stride, bias, act1, mul, mul_dt, mul_stride, act2, out, out_dt, out_stride, cols, total);
+                       in_stride, bias, act1, mul, mul_dt, mul_stride, act2, out, out_dt, out_stride, cols, total,
+                       mul_group);
 }
 
 __global__ void axpby_kernel(float a, const float* x, float b, const float* y, float* out, size_t total) {
@@ -103,7 +107,7 @@ __global__ void __launch_bounds__(1024)
 qkv_rownorm_store_kernel(const TI* qkv, const float* __restrict__ bias, const float* __restrict__ q_norm_w,
                          const float* __restrict__ k_norm_w, const int* __restrict__ slots, TO* q_out, TO* k_cache,
                          TO* v_cache, long long ld, int wq, int wk, int wv, int G, int dk, int dv, int bs, float eps,
-                         int write_kv, int n_slots, int* err) {
+                         int write_kv, int n_slots, int* err, const float2* cs_table, int rot, int pairs) {
     __shared__ float red[33];
     pdl_launch_dependents();
     pdl_wait();
@@ -122,11 +126,28 @@ qkv_rownorm_store_kernel(const TI* qkv, const float* __restrict__ bias, const fl
     sk = block_sum(sk, red);
     const float rq = q_norm_w ? 1.0f / sqrtf(sq / (float)wq + eps) : 1.f;
     const float rk = k_norm_w ? 1.0f / sqrtf(sk / (float)wk + eps) : 1.f;
-    for (int c = tid; c < wq; c += blockDim.x) {
-        float v = to_f<TI>(row[c]) + (bias ? bias[c] : 0.f);
-        if (q_norm_w) v = v * rq * q_norm_w[c];
-        q_out[(size_t)t * wq + c] = from_f<TO>(v);
-    }
+    // The rotation: entry e of a head's first `rot` turns with its partner (e +- rot/2, or its neighbour
+    // in the pair layout) by the token's angle of that pair; a thread reads both normed values.
+    const int half = rot >> 1;
+    const float2* cs = rot ? cs_table + (size_t)t * half : nullptr;
+    auto normed = [&](int base, int c, const float* w, float r) {
+        float v = to_f<TI>(row[base + c]) + (bias ? bias[base + c] : 0.f);
+        if (w) v = v * r * w[c];
+        return v;
+    };
+    auto turned = [&](int base, int c, const float* w, float r) {
+        const float v = normed(base, c, w, r);
+        const int e = c % dk;
+        if (e >= rot) return v;
+        int pair, other;
+        bool first;
+        if (pairs) { pair = e >> 1; first = !(e & 1); other = first ? c + 1 : c - 1; }
+        else { first = e < half; pair = first ? e : e - half; other = first ? c + half : c - half; }
+        const float o = normed(base, other, w, r);
+        const float2 a = cs[pair];
+        return first ? v * a.x - o * a.y : v * a.x + o * a.y;
+    };
+    for (int c = tid; c < wq; c += blockDim.x) q_out[(size_t)t * wq + c] = from_f<TO>(turned(0, c, q_norm_w, rq));
     if (!write_kv) return;
     int slot = slots[t];
     if (slot >= n_slots) {
@@ -135,11 +156,8 @@ qkv_rownorm_store_kernel(const TI* qkv, const float* __restrict__ bias, const fl
     }
     if (slot < 0) return;
     const size_t page = slot / bs, off = slot % bs;
-    for (int c = tid; c < wk; c += blockDim.x) {
-        float v = to_f<TI>(row[wq + c]) + (bias ? bias[wq + c] : 0.f);
-        if (k_norm_w) v = v * rk * k_norm_w[c];
-        k_cache[((page * G + c / dk) * bs + off) * dk + c % dk] = from_f<TO>(v);
-    }
+    for (int c = tid; c < wk; c += blockDim.x)
+        k_cache[((page * G + c / dk) * bs + off) * dk + c % dk] = from_f<TO>(turned(wq, c, k_norm_w, rk));
     for (int c = tid; c < wv; c += blockDim.x) {
         const float v = to_f<TI>(row[wq + wk + c]) + (bias ? bias[wq + wk + c] : 0.f);
         v_cache[((page * G + c / dv) * bs + off) * dv + c % dv] = from_f<TO>(v);
@@ -149,9 +167,11 @@ qkv_rownorm_store_kernel(const TI* qkv, const float* __restrict__ bias, const fl
 RLLM_API int rllm_qkv_rownorm_store(const void* qkv, int in_dt, long long ld, const float* bias, const float* q_norm_w,
                                     const float* k_norm_w, const int* slots, void* q_out, void* k_cache,
                                     void* v_cache, int out_dt, int n, int H, int G, int dk, int dv, int bs,
-                                    float eps, int write_kv, long long n_slots, int* err, cudaStream_t stream) {
+                                    float eps, int write_kv, long long n_slots, int* err, const void* cs_table,
+                                    int rot, int pairs, cudaStream_t stream) {
     if (n <= 0) return 0;
-    if (H <= 0 || G <= 0 || dk <= 0 || dv <= 0 || bs <= 0 || ld < (long long)H * dk + (long long)G * (dk + dv))
+    if (H <= 0 || G <= 0 || dk <= 0 || dv <= 0 || bs <= 0 || ld < (long long)H * dk + (long long)G * (dk + dv) ||
+        rot < 0 || rot > dk || (rot & 1) || (rot && !cs_table))
         return (int)cudaErrorInvalidValue;
     const int ns = (int)(n_slots > 0x7fffffffLL ? 0x7fffffffLL : n_slots);
     // a block per token: few tokens (a decode step) get more threads each, since the row's sums keep it in one block
@@ -159,7 +179,7 @@ RLLM_API int rllm_qkv_rownorm_store(const void* qkv, int in_dt, long long ld, co
 #define LAUNCH(TI, TO)                                                                                         \
     return rllm_launch(qkv_rownorm_store_kernel<TI, TO>, dim3(n), dim3(threads), 0, stream, (const TI*)qkv, bias,  \
                        q_norm_w, k_norm_w, slots, (TO*)q_out, (TO*)k_cache, (TO*)v_cache, ld, H * dk, G * dk, G * dv, \
-                       G, dk, dv, bs, eps, write_kv, ns, err)
+                       G, dk, dv, bs, eps, write_kv, ns, err, (const float2*)cs_table, rot, pairs)
     if (in_dt == RLLM_F32 && out_dt == RLLM_F32) { LAUNCH(float, float); }
     if (in_dt == RLLM_F32 && out_dt == RLLM_BF16) { LAUNCH(float, bf16); }
     if (in_dt == RLLM_BF16 && out_dt == RLLM_BF16) { LAUNCH(bf16, bf16); }

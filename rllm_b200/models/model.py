@@ -84,6 +84,8 @@ class DecoderModel:
                 raise ValueError(f"run entry {i} names layer {e.layer}, but there are {len(self.blocks)}")
             if e.junction is not None and not 0 <= e.junction < len(self.junctions):
                 raise ValueError(f"run entry {i} names junction {e.junction}, but there are {len(self.junctions)}")
+        own = getattr(self.embedding, "cache_need", None)
+        self.embedding_entry = len(self.run_order) if own is not None and own() is not None else None
         self.loaded = False
         # decode steps of this model may be captured into CUDA graphs: every part says it can be
         self.capture_safe = all(getattr(p, "CAPTURE_SAFE", False) for p in self._weighted_parts() + self.blocks)
@@ -140,16 +142,22 @@ class DecoderModel:
 
     # ------------------------------------------------------------------ cache needs
     def cache_needs(self):
-        """(needs, cache_of) per run entry, for the cache manager."""
+        """(needs, cache_of) per run entry, for the cache manager; an embedding that keeps something per
+        request (the previous token of a pair table) comes behind the run entries as one more entry."""
         needs = [self.blocks[e.layer].mixer.cache_need() for e in self.run_order]
-        return needs, [e.cache_of for e in self.run_order]
+        owners = [e.cache_of for e in self.run_order]
+        if self.embedding_entry is not None:
+            needs.append(self.embedding.cache_need())
+            owners.append(None)
+        return needs, owners
 
     # ------------------------------------------------------------------ forward
     def forward(self, ctx, views):
         """Runs the step's tokens through the run order; returns float32 logits [wanted, vocab]
         (None when no row is wanted).  `views[i]` is run entry i's cache view."""
         ctx.scratch = {}                 # what the layers of this pass share (a captured pass makes its own again)
-        x = self.embedding.forward(ctx.tokens)
+        at = self.embedding_entry
+        x = self.embedding.forward(ctx.tokens) if at is None else self.embedding.forward(ctx.tokens, ctx, views[at])
         x0 = x.clone() if self.junctions else None       # the embedding output, for the junctions
         pending = None
         from ..csrc import ops

@@ -15,8 +15,9 @@ model's final norm, or a junction, for the last one).  A layer whose spec has no
 has the mixer sublayer only.  Such blocks take the plain path below (no deferred norms, no
 accumulation into the stream by the products).
 
-``post_norm`` (further down) puts the norms on the sublayers' outputs instead, ``sandwich_norm`` (at the
-end of this file) on both sides of each sublayer.
+``post_norm`` (further down) puts the norms on the sublayers' outputs instead, ``sandwich_norm`` on both
+sides of each sublayer, and ``sum_norm`` (at the end of this file) behind the residual sums, so that the
+normed rows are the stream.
 
 A block's interface: ``__init__(layer_spec, runtime)`` builds its parts from the registries;
 ``parts()`` lists them; ``forward(x, pending, ctx, cache) -> pending``.
@@ -241,3 +242,47 @@ class SandwichNormBlock:
         f = self.ffn.forward(h, ctx)
         h = self._join(self.norm_ffn_out, x, f, nxt)
         return PreparedRows(h) if h is not None else None
+
+
+@register_part("block", "sum_norm")
+class SumNormBlock:
+    """The norm stands AFTER the residual sum and its result is the stream:
+
+        x <- norm_mixer(alpha * x + mixer(x));  x <- norm_ffn(alpha * x + ffn(x))     (no feed-forward: the first only)
+
+    with `alpha` a constant of the model (block parameter, default 1).  The sublayers read the stream
+    itself; the stream, the sum and the norm are float32, and a product's operand is the stream rounded to
+    the activation type, which the kernel that norms a sum writes beside the stream (the first block of a
+    pass makes its own copy).  Nothing is owed to the stream when the block returns."""
+
+    CAPTURE_SAFE = True
+    TRACEABLE = False
+    DEFERS_NORM = False
+
+    def __init__(self, layer_spec, runtime):
+        self.runtime = runtime
+        self.alpha = float(dict(getattr(layer_spec, "block_params", None) or {}).get("alpha", 1.0))
+        self.norm_mixer = build_part("norm", layer_spec.norms["mixer"], runtime)
+        self.mixer = build_part("mixer", layer_spec.mixer, runtime)
+        self.ffn = build_part("ffn", layer_spec.ffn, runtime) if layer_spec.ffn is not None else None
+        self.norm_ffn = build_part("norm", layer_spec.norms["ffn"], runtime) if self.ffn is not None else None
+        self.position = (build_part("position", layer_spec.position, runtime)
+                         if layer_spec.position is not None else None)
+        for nm in (self.norm_mixer, self.norm_ffn):
+            if nm is not None and not hasattr(nm, "sum_norm"):
+                raise ValueError("sum_norm: the norm part must offer sum_norm(x, y, alpha, copy)")
+        self.CAPTURE_SAFE = all(getattr(p, "CAPTURE_SAFE", False) for p in self.parts())
+
+    parts = OutputNormBlock.parts
+    _operand = OutputNormBlock._operand
+
+    def forward(self, x, pending, ctx, cache):
+        if pending is not None:
+            raise ValueError("sum_norm: the block before still owes the stream something; it joins its outputs itself")
+        h, copy = self._operand(x, ctx)
+        a = self.mixer.forward(h, ctx, cache, self.position)
+        self.norm_mixer.sum_norm(x, a, self.alpha, copy)        # x and its copy are the new stream
+        if self.ffn is not None:
+            f = self.ffn.forward(h, ctx)
+            self.norm_ffn.sum_norm(x, f, self.alpha, copy)
+        return None

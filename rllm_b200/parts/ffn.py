@@ -97,7 +97,10 @@ class ClampedGLU(FeedForward):
         g = min(h . Wg^T, limit),  u = clamp(h . Wu^T, -limit, limit)
         out = (g * sigmoid(alpha * g) * (u + shift)) . Wd^T
 
-    Parameters: hidden_size, intermediate_size, limit (0: no clamp), alpha, shift.  Tensors
+    With `activation` "gelu_tanh" the gate's factor g sigmoid(alpha g) is the tanh form of gelu instead,
+    0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) (alpha is then not used).
+
+    Parameters: hidden_size, intermediate_size, limit (0: no clamp), alpha, shift, activation.  Tensors
     <prefix>gate, <prefix>up, <prefix>down; gate and up are stacked into one [2F, hidden] matrix."""
     CAPTURE_SAFE = True
 
@@ -108,6 +111,13 @@ class ClampedGLU(FeedForward):
         self.limit = float(params.get("limit", 0.0) or 0.0)
         self.alpha = float(params.get("alpha", 1.0))
         self.shift = float(params.get("shift", 0.0))
+        act = params.get("activation") or "sigmoid"
+        if act not in ("sigmoid", "gelu_tanh"):
+            raise ValueError(f"clamped_glu: activation {act!r} is not known ('sigmoid', 'gelu_tanh')")
+        if act == "gelu_tanh":
+            self.alpha = ops.GLU_GELU_TANH[1]           # the kernels' mark for the tanh form of gelu
+        elif self.alpha == 0.0:
+            raise ValueError("clamped_glu: alpha must not be 0")
         self.w_gate_up = self.w_down = None
 
     def expected_tensors(self):

@@ -2,7 +2,9 @@
 
 For normed input rows h [n, d], E experts of size F, each token using `top_k`:
 
-    z = h Wr^T  (float32);  s = sigmoid(z)  (or softmax over the experts: `score`)
+    z = h Wr^T (+ a stored bias per expert: `router_bias`)  (float32);  s = sigmoid(z)  (or softmax over the
+        experts: `score`; softmax scores of the chosen experts divided by their sum are the softmax over the
+        chosen logits alone)
     choice scores c = s + correction                     (`correction`: a stored vector, else none)
     experts form `n_groups` equal groups of neighbours; a group's score is the sum of its `group_best`
         largest c; only experts of the `keep_groups` best groups can be chosen (the others count as
@@ -15,8 +17,8 @@ For normed input rows h [n, d], E experts of size F, each token using `top_k`:
                                                           for every token; `shared_gate`: its gate)
 
 Parameters: hidden_size, intermediate_size, num_experts, top_k, n_groups, keep_groups, group_best, score,
-correction, normalize, weight_eps, route_scale, shared_size, shared_gate.  Tensors under <prefix>:
-router [E, d], correction [E], e<i>.gate, e<i>.up [F, d], e<i>.down [d, F], shared.gate, shared.up,
+correction, normalize, weight_eps, route_scale, shared_size, shared_gate, router_bias.  Tensors under <prefix>:
+router [E, d], router.b [E], correction [E], e<i>.gate, e<i>.up [F, d], e<i>.down [d, F], shared.gate, shared.up,
 shared.down, shared.sg [1, d].  Load-time transform: the experts' matrices are stacked ([E, 2F, d] gate
 rows then up rows, [E, d, F]), and the shared expert's gate row is stacked under the router's so that
 one product gives both (with rows of zeros up to a multiple of 8 rows).  The router's logits, scores, choice
@@ -50,6 +52,7 @@ class RoutedExperts(FeedForward):
         self.group_best = int(p.get("group_best", 2))
         self.score = p.get("score", "sigmoid")
         self.has_correction = bool(p.get("correction", False))
+        self.has_bias = bool(p.get("router_bias", False))
         self.normalize = bool(p.get("normalize", True))
         self.weight_eps = float(p.get("weight_eps", 0.0))
         self.route_scale = float(p.get("route_scale", 1.0))
@@ -60,6 +63,7 @@ class RoutedExperts(FeedForward):
                             f"of which {self.keep_groups} are kept")
         if not 0 < self.top_k <= self.keep_groups * (self.E // self.n_groups):
             raise PartError(f"routed_experts: top_k {self.top_k} exceeds the experts of the kept groups")
+        self.router_bias = None
         self.w_router = self.correction = self.w_gu = self.w_down = self.w_shared_gu = self.w_shared_down = None
 
     def expected_tensors(self):
@@ -67,6 +71,8 @@ class RoutedExperts(FeedForward):
         t = {p + "router": ((self.E, d), "matrix")}
         if self.has_correction:
             t[p + "correction"] = ((self.E,), "unit")
+        if self.has_bias:
+            t[p + "router.b"] = ((self.E,), "unit")
         for e in range(self.E):
             t.update({f"{p}e{e}.gate": ((F, d), "matrix"), f"{p}e{e}.up": ((F, d), "matrix"),
                       f"{p}e{e}.down": ((d, F), "matrix")})
@@ -89,6 +95,8 @@ class RoutedExperts(FeedForward):
         self.w_router = self._to_device(torch.cat(router, 0))
         if self.has_correction:
             self.correction = self._to_device(tensors[p + "correction"], torch.float32)
+        if self.has_bias:
+            self.router_bias = self._to_device(tensors[p + "router.b"], torch.float32)
         self.w_gu = self._to_device(torch.stack(
             [torch.cat([tensors[f"{p}e{e}.gate"].to(dt), tensors[f"{p}e{e}.up"].to(dt)], 0) for e in range(self.E)], 0))
         self.w_down = self._to_device(torch.stack([tensors[f"{p}e{e}.down"].to(dt) for e in range(self.E)], 0))
@@ -104,7 +112,7 @@ class RoutedExperts(FeedForward):
         idx = torch.empty((n, self.top_k), dtype=torch.int32, device=dev)
         weight = torch.empty((n, self.top_k), dtype=torch.float32, device=dev)
         ops.moe_route(logits, self.correction, idx, weight, self.E, self.top_k, self.n_groups, self.keep_groups,
-                      self.group_best, self.score, self.normalize, self.weight_eps, self.route_scale)
+                      self.group_best, self.score, self.normalize, self.weight_eps, self.route_scale, bias=self.router_bias)
         return idx, weight, logits
 
     def forward(self, h, ctx=None, residual=None):

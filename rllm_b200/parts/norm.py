@@ -7,7 +7,7 @@ crates/rllm-cuda/kernels/kernels.cu:794-820 and crates/rllm-model/src/qwen3.rs:2
 Parameters: size, eps, optionally `tensor` (the weight's full name) and `one_plus` (the stored
 weight lies around zero and multiplies as 1 + w; the sum is formed once, in float32, at load).  Tensor: <prefix>weight
 [size], kept in float32.  `delta_scale`: the delta joins the stream multiplied by it.  `join(x, y)`: the norm of a sublayer's
-output, x += norm(y) * weight.
+output, x += norm(y) * weight.  `sum_norm(x, y, alpha)`: the norm behind the sum, x = norm(alpha x + y) * weight.
 """
 from __future__ import annotations
 
@@ -47,6 +47,12 @@ class RMSNorm(Norm):
         stream `x` (in place).  `copy`, if given, also takes the new x in its own type (the operand of
         the next product).  Returns `copy`, or x."""
         return ops.norm_rows(y, self.weight, self.eps, x=x, add=True, low=copy)
+
+    def sum_norm(self, x, y, alpha=1.0, copy=None):
+        """x <- (alpha * x + y) / rms(alpha * x + y) * weight: the norm stands behind the residual sum and
+        the normed rows are the float32 stream `x` (in place); `copy`, if given, also takes them in its own
+        type (the operand of the next product)."""
+        return ops.sum_norm_rows(x, y, alpha, self.weight, self.eps, low=copy)
 
     def join_then(self, x, y, nxt):
         """x += y / rms(y) * weight, and in the same kernel the rows of the norm `nxt` of the new x (in

@@ -91,8 +91,12 @@ class RotaryScaled(Part):
     dim(t) = dims * ln(original / (2 pi t)) / (2 ln base), lo = max(floor(dim(fast)), 0),
     hi = min(ceil(dim(slow)), dims - 1), ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1); pair
     i then turns with f_i / factor * ramp_i + f_i * (1 - ramp_i), and cos and sin are multiplied by
-    `mult` = 0.1 ln(factor) + 1.  Frequencies are worked out in double precision on the host and
-    rounded once; angles (position * frequency), cos and sin are float32 on the device.
+    `mult` = 0.1 ln(factor) + 1.  With `scaling` = {factor, low, high, original} (the long-context rule
+    of Llama 3.1) a pair's wavelength l = 2 pi / f_i decides: l < original / high keeps f_i; l >
+    original / low turns with f_i / factor; between the two, with s = (original / l - low) / (high - low),
+    with (1 - s) f_i / factor + s f_i; cos and sin are not multiplied.  Frequencies are worked out in
+    double precision on the host and rounded once; angles (position * frequency), cos and sin are float32
+    on the device.
 
     Parameters: dims, base, scaling (or None), layout.  No tensors.  The part offers `table()` (the
     frequencies), `mult` and `angles(ctx)` (cos, sin per token and pair, once per pass) to mixers whose
@@ -112,7 +116,18 @@ class RotaryScaled(Part):
         f = [self.base ** (-2.0 * i / self.dims) for i in range(half)]
         self.mult = 1.0
         sc = params.get("scaling")
-        if sc:
+        if sc and "low" in sc:
+            factor, original, low, high = (float(sc[k]) for k in ("factor", "original", "low", "high"))
+            if not high > low > 0 or not factor > 0 or not original > 0:
+                raise PartError("rotary_scaled: scaling needs factor > 0, original > 0 and high > low > 0")
+            for i in range(half):
+                wave = 2.0 * math.pi / f[i]
+                if wave > original / low:
+                    f[i] = f[i] / factor
+                elif wave >= original / high:
+                    s = (original / wave - low) / (high - low)
+                    f[i] = (1.0 - s) * f[i] / factor + s * f[i]
+        elif sc:
             factor, original = float(sc["factor"]), float(sc["original"])
 
             def dim_of(turns):
