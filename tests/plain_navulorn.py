@@ -113,7 +113,7 @@ def attention(h, w, pre, mx, eps):
     f = frequencies(rot["dims"], rot["base"], rot.get("scaling"))
     pos = torch.arange(n)
     q, k = rotate(q, pos, f, rot["dims"], "half"), rotate(k, pos, f, rot["dims"], "half")
-    a = window_softmax_attention(q, k, v, mx["scale"], mx["mask"]["size"], H // G)
+    a = window_softmax_attention(q, k, v, mx["scale"], (mx.get("mask") or {}).get("size", 0), H // G)
     gate = torch.sigmoid(h @ w[pre + "g"].T)                      # [n, H]
     a = a * gate[:, :, None]
     return a.reshape(n, H * dv) @ w[pre + "o"].T
@@ -136,7 +136,7 @@ def latent_attention(h, w, pre, mx, eps):
     v = (c @ w[pre + "uv"].T).view(n, H, dv)
     qq = torch.cat([q[..., :dk], q_rot], -1)
     kk = torch.cat([k_plain, kr.expand(n, H, r)], -1)
-    a = window_softmax_attention(qq, kk, v, mx["scale"], mx["mask"]["size"], 1)
+    a = window_softmax_attention(qq, kk, v, mx["scale"], (mx.get("mask") or {}).get("size", 0), 1)
     return a.reshape(n, H * dv) @ w[pre + "o"].T
 
 
@@ -172,16 +172,31 @@ def dense_ff(h, w, pre):
     return (gelu_tanh(h @ w[pre + "gate"].T) * (h @ w[pre + "up"].T)) @ w[pre + "down"].T
 
 
-def route(h, w, pre, top):
-    """(chosen experts [n, top], their weights [n, top]): the largest logits, softmax over them alone."""
+def route(h, w, pre, top, given=None, slack=0.0, margins=None):
+    """(chosen experts [n, top], their weights [n, top]): the largest logits, softmax over them alone.
+    `margins` (a list) takes, per token, how far the choice is from another one (the gap between the last
+    chosen logit and the best one left out).  `given` {token index: experts}: somebody else's choice is taken
+    over for a token when it is what this router gives after moving every logit by at most `slack`."""
     z = h @ w[pre + "router"].T + w[pre + "router.b"]
     val, idx = torch.topk(z, top, dim=-1)
+    E = z.shape[1]
+    if margins is not None:
+        rest = torch.topk(z, top + 1, dim=-1).values[:, -1] if top < E else torch.full((z.shape[0],), -math.inf, dtype=F64)
+        margins.append([float(x) for x in (val[:, -1] - rest)])
+    for t, cand in (given or {}).items():
+        cand = [int(c) for c in cand]
+        if t >= z.shape[0] or len(set(cand)) != top or sorted(cand) == sorted(idx[t].tolist()):
+            continue
+        out = [e for e in range(E) if e not in cand]
+        if not out or float(z[t, cand].min()) + 2 * slack >= float(z[t, out].max()):
+            idx[t] = torch.tensor(cand)
+            val[t] = z[t, cand]
     return idx, torch.softmax(val, -1), z
 
 
-def moe_ff(h, w, pre, mlp):
+def moe_ff(h, w, pre, mlp, given=None, slack=0.0, margins=None):
     top = mlp["router"]["top"]
-    idx, wt, _ = route(h, w, pre, top)
+    idx, wt, _ = route(h, w, pre, top, given, slack, margins)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for j in range(top):
@@ -195,26 +210,31 @@ def moe_ff(h, w, pre, mlp):
 MIXERS = {"attention": attention, "latent_attention": latent_attention, "mlstm": mlstm}
 
 
-def layer(x, w, i, spec, cfg):
-    eps, alpha = cfg["norm"]["eps"], cfg["postln_alpha"]
+def layer(x, w, i, spec, cfg, given=None, slack=0.0, margins=None):
+    eps, alpha = cfg["norm"]["eps"], cfg.get("postln_alpha", 1.0)
     a = MIXERS[spec["type"]](x, w, f"l{i}.mix.", spec["mixer"], eps)
     x = rms_norm(alpha * x + a, w[f"l{i}.norm1"], eps)
     mlp = spec.get("mlp")
     if mlp is not None:
-        f = dense_ff(x, w, f"l{i}.mlp.") if mlp["kind"] == "dense" else moe_ff(x, w, f"l{i}.mlp.", mlp)
+        f = (dense_ff(x, w, f"l{i}.mlp.") if mlp["kind"] == "dense"
+             else moe_ff(x, w, f"l{i}.mlp.", mlp, (given or {}).get(i), slack, margins))
         x = rms_norm(alpha * x + f, w[f"l{i}.norm2"], eps)
     return x
 
 
-def forward(cfg, weights, tokens, streams=None):
+def forward(cfg, weights, tokens, streams=None, margins=None, given=None, slack=0.0):
     """Logits [n, vocab] (float64) of one sequence from its start.  `weights`: name -> tensor of any
-    float type; `streams`, if a list, takes the stream after every layer."""
+    float type; `streams`, if a list, takes the stream after every layer; `margins`, `given`, `slack`: see
+    `route` (`given` is {layer: {token index: experts}})."""
     w = {k: v.to(F64) for k, v in weights.items()}
-    e = cfg["embedding"]
-    b = e["bigram"]
-    x = embed(tokens, w["embed"], w["bigram"], e["scale"], b["buckets"], b["mul_prev"], b["mul_cur"])
+    e = cfg.get("embedding") or {}
+    b = e.get("bigram")
+    if b:
+        x = embed(tokens, w["embed"], w["bigram"], e.get("scale", 1.0), b["buckets"], b["mul_prev"], b["mul_cur"])
+    else:
+        x = w["embed"][torch.tensor(list(tokens), dtype=torch.long)] * e.get("scale", 1.0)
     for i, spec in enumerate(cfg["layers"]):
-        x = layer(x, w, i, spec, cfg)
+        x = layer(x, w, i, spec, cfg, given, slack, margins)
         if streams is not None:
             streams.append(x.clone())
     x = rms_norm(x, w["final.norm"], cfg["norm"]["eps"])
