@@ -91,8 +91,8 @@ CASES = {
                      mem(2, 24, 40, cap=10.0, mlp=moe(16, 6, 2)),
                      lat(2, 8, 8, 8, 16, 11)], width=64, vocab=131, alpha=2.5, scale=4.0),
     "stack_attention_first": config([att(4, 4, 8, 10, 2, 10, mlp=moe(20, 4, 2)), lat(3, 10, 6, 6, 12, 25, mlp=dense(36)),
-                                     mem(3, 12, 6, cap=6.0), att(3, 1, 20, 10, 10, 40, mlp=dense(36))], width=40,
-                                    vocab=89, alpha=1.0, bigram=(53, 2, 9)),
+                                     mem(3, 12, 18, cap=6.0), att(3, 1, 20, 10, 10, 40, mlp=dense(36))], width=40,
+                                    vocab=89, alpha=2.0, bigram=(53, 2, 9)),
 }
 
 
@@ -177,9 +177,15 @@ def oracle(cfg, weights, tokens, streams=None, given=None, slack=0.0):
     """float64 logits [T, vocab] of the plain implementation from the weights as stored.  The result
     carries `margin` [T], how far each token's choice of experts is from another choice (the smallest
     over the layers of routed experts, infinite without any), and `again(given, slack)`: the logits once
-    more with somebody else's choices taken over where they are as good as the plain router's own."""
+    more with somebody else's choices taken over where they are as good as the plain router's own.  For
+    weights stored in bfloat16 it also carries `noise` [T]: how far each row moves when every sublayer reads
+    and returns rows rounded to bfloat16 (what rounding alone does to the row, with exact arithmetic)."""
     margins = []
     logits = plain_navulorn.forward(cfg, weights, tokens, streams, margins=margins, given=given, slack=slack)
+    if weights["embed"].dtype == torch.bfloat16:
+        coarse = plain_navulorn.forward(cfg, weights, tokens, given=given, slack=slack,
+                                        coarse=lambda t: t.to(torch.bfloat16).to(torch.float64))
+        logits.noise = [row_error(coarse[p], logits[p]) for p in range(len(tokens))]
     m = torch.full((len(tokens),), math.inf, dtype=torch.float64)
     for per_token in margins:
         m = torch.minimum(m, torch.tensor(per_token, dtype=torch.float64))

@@ -210,22 +210,25 @@ def moe_ff(h, w, pre, mlp, given=None, slack=0.0, margins=None):
 MIXERS = {"attention": attention, "latent_attention": latent_attention, "mlstm": mlstm}
 
 
-def layer(x, w, i, spec, cfg, given=None, slack=0.0, margins=None):
+def layer(x, w, i, spec, cfg, given=None, slack=0.0, margins=None, coarse=None):
+    """`coarse`, if given, is applied to what every sublayer reads and to what it returns: the stream as a
+    sublayer with operands of fewer bits sees it (the stream itself and its sums keep their precision)."""
     eps, alpha = cfg["norm"]["eps"], cfg.get("postln_alpha", 1.0)
-    a = MIXERS[spec["type"]](x, w, f"l{i}.mix.", spec["mixer"], eps)
+    see = coarse or (lambda t: t)
+    a = see(MIXERS[spec["type"]](see(x), w, f"l{i}.mix.", spec["mixer"], eps))
     x = rms_norm(alpha * x + a, w[f"l{i}.norm1"], eps)
     mlp = spec.get("mlp")
     if mlp is not None:
-        f = (dense_ff(x, w, f"l{i}.mlp.") if mlp["kind"] == "dense"
-             else moe_ff(x, w, f"l{i}.mlp.", mlp, (given or {}).get(i), slack, margins))
-        x = rms_norm(alpha * x + f, w[f"l{i}.norm2"], eps)
+        f = (dense_ff(see(x), w, f"l{i}.mlp.") if mlp["kind"] == "dense"
+             else moe_ff(see(x), w, f"l{i}.mlp.", mlp, (given or {}).get(i), slack, margins))
+        x = rms_norm(alpha * x + see(f), w[f"l{i}.norm2"], eps)
     return x
 
 
-def forward(cfg, weights, tokens, streams=None, margins=None, given=None, slack=0.0):
+def forward(cfg, weights, tokens, streams=None, margins=None, given=None, slack=0.0, coarse=None):
     """Logits [n, vocab] (float64) of one sequence from its start.  `weights`: name -> tensor of any
     float type; `streams`, if a list, takes the stream after every layer; `margins`, `given`, `slack`: see
-    `route` (`given` is {layer: {token index: experts}})."""
+    `route` (`given` is {layer: {token index: experts}}); `coarse`: see `layer`."""
     w = {k: v.to(F64) for k, v in weights.items()}
     e = cfg.get("embedding") or {}
     b = e.get("bigram")
@@ -234,11 +237,11 @@ def forward(cfg, weights, tokens, streams=None, margins=None, given=None, slack=
     else:
         x = w["embed"][torch.tensor(list(tokens), dtype=torch.long)] * e.get("scale", 1.0)
     for i, spec in enumerate(cfg["layers"]):
-        x = layer(x, w, i, spec, cfg, given, slack, margins)
+        x = layer(x, w, i, spec, cfg, given, slack, margins, coarse)
         if streams is not None:
             streams.append(x.clone())
     x = rms_norm(x, w["final.norm"], cfg["norm"]["eps"])
-    logits = x @ w["head"].T
+    logits = (coarse(x) if coarse else x) @ w["head"].T
     cap = cfg.get("logit_softcap")
     if cap:
         logits = cap * torch.tanh(logits / cap)
