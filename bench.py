@@ -172,7 +172,33 @@ def divuzen_shape(width: int) -> dict:
             "logit_scale": 0.5}
 
 
-FAMILY_SHAPES = {"falalix": falalix_shape, "govopel": govopel_shape, "divuzen": divuzen_shape}
+def navulorn_shape(width: int) -> dict:
+    """A Navulorn configuration with layer sizes of a real model of that width: the matrix memory
+    (width/128 heads of 128 x 128, gates capped at 15; dense feed-forward of 3 widths with the tanh form of
+    gelu), windowed attention (width/128 heads of 128, a quarter as many key/value heads, half of each head
+    rotated with the long-context frequency rule, a window of 1,024 keys, a gate per head; 16 routed experts
+    of 3/8 width of which a token uses 4), windowed attention through a latent of 512 + 64 entries (heads of
+    128 + 64, values of 128) with routed experts, attention again with a dense feed-forward; that order
+    twice: eight layer runs.  Pair table of 32,749 buckets."""
+    heads = max(8, width // 128)
+    dense = {"kind": "dense", "ff": 3 * width}
+    moe = {"kind": "moe", "expert": {"ff": 3 * width // 8}, "router": {"experts": 16, "top": 4}}
+    mem = {"heads": max(4, width // 128), "dim": 128, "vdim": 128, "gate_cap": 15.0}
+    att = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "mask": {"size": 1024},
+           "rot": {"dims": 64, "base": 500000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}},
+           "scale": 128 ** -0.5}
+    lat = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "mask": {"size": 1024},
+           "rot": {"dims": 64, "base": 10000.0}, "scale": 192 ** -0.5}
+    layers = [{"type": "mlstm", "mixer": mem, "mlp": dense}, {"type": "attention", "mixer": att, "mlp": moe},
+              {"type": "latent_attention", "mixer": lat, "mlp": moe}, {"type": "attention", "mixer": att, "mlp": dense}] * 2
+    return {"architecture": "Navulorn", "vocab": 32768, "width": width, "layers": layers, "norm": {"eps": 1e-6},
+            "embedding": {"scale": 8.0, "bigram": {"buckets": 32749, "mul_prev": 31, "mul_cur": 7}}, "postln_alpha": 2.0,
+            "logit_softcap": 30.0}
+
+
+FAMILY_SHAPES = {"falalix": falalix_shape, "govopel": govopel_shape, "divuzen": divuzen_shape, "navulorn": navulorn_shape}
+# the model a family stands beside: Qwen3-shaped of equal width, depth and feed-forward, unless another family is closer
+BESIDE = {"navulorn": "divuzen"}
 
 
 def falalix_compare(a):
@@ -189,7 +215,8 @@ def falalix_compare(a):
     g = torch.Generator().manual_seed(1)
     widths = {"1k": 1024, "2k": 2048, "4k": 4096}
     family = a.workload
-    out = {"metric": f"{family.capitalize()}-shaped against Qwen3-shaped models of equal width and depth: prefill tok/s "
+    other = BESIDE.get(family, "qwen3")
+    out = {"metric": f"{family.capitalize()}-shaped against {other.capitalize()}-shaped models of equal width and depth: prefill tok/s "
                      "(2,048 tokens, one step) and decode tok/s (batch 8, 2,048-token prompts)",
            "unit": "tok/s", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup, "dtype": "bf16", "impl": "ours",
            "data": "synthetic: random weights, uniform random token ids", "sizes": {}}
@@ -199,12 +226,13 @@ def falalix_compare(a):
     for size in a.sizes.split(","):
         width = widths[size]
         row = {}
-        for name in (family, "qwen3"):
+        for name in (family, other):
             fal = FAMILY_SHAPES[family](width)
             runs = len(fal["layers"])
             if fal.get("loop"):
                 runs += (fal["loop"]["stop"] - fal["loop"]["start"]) * (fal["loop"]["times"] - 1)
-            config = config_from_dict(fal if name == family else qwen3_shape(width, runs))
+            config = config_from_dict(fal if name == family else
+                                      FAMILY_SHAPES[other](width) if other in FAMILY_SHAPES else qwen3_shape(width, runs))
             model = random_model(config, seed=0, dtype="bfloat16", device="cuda:0", generate_on_device=True)
             V = model.spec.vocab_size
             eng = Engine(model, block_size=32, max_tokens=a.batch * (PROMPT + 256), max_requests=a.batch)
@@ -283,13 +311,14 @@ def main():
     ap.add_argument("--ctx", type=int, default=None, help="tokens a request may hold (default: twice the prompt)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 / 64 and prefill")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "falalix", "govopel", "divuzen"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "falalix", "govopel", "divuzen", "navulorn"],
                     help="decode: the default line.  serving: --requests prompts of 16..2,048 tokens with 128..512 "
                          "generated tokens each through LLM.generate (continuous batching), one line of its own.  "
                          "falalix: prefill and decode of Falalix-shaped models (--sizes) beside Qwen3-shaped models of "
-                         "equal width, depth and feed-forward, one line of its own.  govopel: the same for "
-                         "Govopel-shaped and for Divuzen-shaped models")
-    ap.add_argument("--sizes", default="1k,2k,4k", help="falalix, govopel, divuzen: model widths to run (1k, 2k, 4k)")
+                         "equal width, depth and feed-forward, one line of its own.  govopel, divuzen: the same for "
+                         "Govopel-shaped and for Divuzen-shaped models.  navulorn: Navulorn-shaped beside Divuzen-shaped "
+                         "models of equal width and depth")
+    ap.add_argument("--sizes", default="1k,2k,4k", help="falalix, govopel, divuzen, navulorn: model widths to run (1k, 2k, 4k)")
     ap.add_argument("--requests", type=int, default=64)
     ap.add_argument("--parallel", type=int, default=32, help="serving: requests running at once")
     ap.add_argument("--prefill-chunk", type=int, default=512, help="serving: prompt tokens per step")
