@@ -312,11 +312,77 @@ sum_norm_rows_kernel(float* x, float alpha, const void* y, int y_dt, long long l
     }
 }
 
+// The same for float32 y whose rows, weight and outputs allow 16-byte accesses (d and the row strides multiples
+// of 4): the row is read once and kept in registers, four columns a thread and pass.  Which of the two
+// kernels runs depends on the sizes and addresses only, never on the batch.
+template <typename TL, int NV>
+__global__ void __launch_bounds__(256)
+sum_norm_rows_vec_kernel(float* x, float alpha, const float* y, long long ld_y, const float* __restrict__ w, TL* low,
+                         long long ld_low, int d, float eps) {
+    __shared__ float red[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t t = blockIdx.x;
+    const int d4 = d >> 2;
+    float4* x4 = reinterpret_cast<float4*>(x + t * d);
+    const float4* y4 = reinterpret_cast<const float4*>(y + t * ld_y);
+    const float4* w4 = reinterpret_cast<const float4*>(w);
+    float4 v[NV];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int i = k * 256 + threadIdx.x;
+        if (i < d4) {
+            const float4 a = x4[i], b = y4[i];
+            v[k] = make_float4(alpha * a.x + b.x, alpha * a.y + b.y, alpha * a.z + b.z, alpha * a.w + b.w);
+        } else {
+            v[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+    }
+    ss = block_sum(ss, red);
+    const float rs = 1.0f / sqrtf(ss / (float)d + eps);
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int i = k * 256 + threadIdx.x;
+        if (i < d4) {
+            const float4 g = w4[i];
+            const float4 o = make_float4(v[k].x * rs * g.x, v[k].y * rs * g.y, v[k].z * rs * g.z, v[k].w * rs * g.w);
+            x4[i] = o;
+            if (low) {
+                TL* lp = low + t * ld_low + 4 * (size_t)i;
+                lp[0] = from_f<TL>(o.x); lp[1] = from_f<TL>(o.y); lp[2] = from_f<TL>(o.z); lp[3] = from_f<TL>(o.w);
+            }
+        }
+    }
+}
+
+template <typename TL>
+static int launch_sum_norm_vec(int n, int d, cudaStream_t stream, float* x, float alpha, const float* y, long long ld_y,
+                               const float* w, TL* low, long long ld_low, float eps) {
+#define SV(NV)                                                                                                    \
+    return rllm_launch(sum_norm_rows_vec_kernel<TL, NV>, dim3(n), dim3(256), 0, stream, x, alpha, y, ld_y, w, low, \
+                       ld_low, d, eps)
+    const int nv = (d / 4 + 255) / 256;
+    if (nv <= 1) { SV(1); }
+    if (nv <= 2) { SV(2); }
+    if (nv <= 4) { SV(4); }
+    if (nv <= 8) { SV(8); }
+    SV(16);
+#undef SV
+}
+
 RLLM_API int rllm_sum_norm_rows(float* x, float alpha, const void* y, int y_dt, long long ld_y, const float* w,
                                 void* low, int low_dt, long long ld_low, int n, int d, float eps,
                                 cudaStream_t stream) {
     if (n <= 0) return 0;
     if (d <= 0 || !x || !y || !w || ld_y < d || (low && ld_low < d)) return (int)cudaErrorInvalidValue;
+    const auto al16 = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+    if (y_dt == RLLM_F32 && d >= 256 && d <= 16384 && (d & 3) == 0 && (ld_y & 3) == 0 && al16(x) && al16(y) && al16(w)) {
+        if (!low || low_dt == RLLM_F32)
+            return launch_sum_norm_vec<float>(n, d, stream, x, alpha, (const float*)y, ld_y, w, (float*)low, ld_low, eps);
+        return launch_sum_norm_vec<bf16>(n, d, stream, x, alpha, (const float*)y, ld_y, w, (bf16*)low, ld_low, eps);
+    }
     return rllm_launch(sum_norm_rows_kernel, dim3(n), dim3(d >= 1024 ? 256 : 128), 0, stream, x, alpha, y, y_dt, ld_y,
                        w, low, low_dt, ld_low, d, eps);
 }

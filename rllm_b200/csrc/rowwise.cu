@@ -50,12 +50,40 @@ __global__ void rows_act_kernel(const void* in, int in_dt, long long in_stride, 
     st_any(out, out_dt, t * out_stride + c, v);
 }
 
+// The gate of an attention's heads on bfloat16 rows: out[t, c] = in[t, c] * f2(mul[t, c / group]) with eight
+// columns (16 bytes) a thread; `group` a multiple of 8, so the eight share a factor.
+__global__ void rows_gate_bf16_kernel(const bf16* in, long long in_stride, const float* mul, long long mul_stride, int act2,
+                                      bf16* out, long long out_stride, int cols8, int group8, size_t total) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const size_t t = i / cols8;
+    const int c8 = (int)(i - t * cols8);
+    const float f = act_apply(mul[t * mul_stride + c8 / group8], act2);
+    uint4 u = *reinterpret_cast<const uint4*>(in + t * in_stride + 8 * (size_t)c8);
+    __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const float2 v = __bfloat1622float2(p[q]);
+        p[q] = __floats2bfloat162_rn(v.x * f, v.y * f);
+    }
+    *reinterpret_cast<uint4*>(out + t * out_stride + 8 * (size_t)c8) = u;
+}
+
 RLLM_API int rllm_rows_act(const void* in, int in_dt, long long in_stride, const float* bias, int act1,
                            const void* mul, int mul_dt, long long mul_stride, int act2, void* out, int out_dt,
                            long long out_stride, int n, int cols, int mul_group, cudaStream_t stream) {
     const size_t total = (size_t)n * cols;
     if (total == 0) return 0;
     if (mul_group <= 0) return (int)cudaErrorInvalidValue;
+    const auto al16 = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+    if (in_dt == RLLM_BF16 && out_dt == RLLM_BF16 && mul && mul_dt == RLLM_F32 && !bias && act1 == ACT_NONE &&
+        mul_group % 8 == 0 && cols % 8 == 0 && in_stride % 8 == 0 && out_stride % 8 == 0 && al16(in) && al16(out)) {
+        const size_t t8 = total / 8;
+        return rllm_launch(rows_gate_bf16_kernel, dim3((unsigned)((t8 + 255) / 256)), dim3(256), 0, stream, (const bf16*)in,
+                           in_stride, (const float*)mul, mul_stride, act2, (bf16*)out, out_stride, cols / 8, mul_group / 8, t8);
+    }
     return rllm_launch(rows_act_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, in, in_dt,
                        in_stride, bias, act1, mul, mul_dt, mul_stride, act2, out, out_dt, out_stride, cols, total,
                        mul_group);
@@ -102,13 +130,16 @@ RLLM_API int rllm_cat2_cast(const float* x, const void* delta, int delta_dt, flo
 // column when the weight is given; q -> q_out[t]; k, v -> the paged cache at slots[t]
 // (layouts [page][kv_head][bs][dk] and [page][kv_head][bs][dv]); slot < 0 writes nothing, a slot
 // beyond the pool sets the error word.
-template <typename TI, typename TO>
+// STAGED: the q and k columns (with their bias) are read from global memory once, into shared memory
+// ((wq + wk) floats), and the norm, the rotation and its partner reads work from there.
+template <typename TI, typename TO, bool STAGED>
 __global__ void __launch_bounds__(1024)
 qkv_rownorm_store_kernel(const TI* qkv, const float* __restrict__ bias, const float* __restrict__ q_norm_w,
                          const float* __restrict__ k_norm_w, const int* __restrict__ slots, TO* q_out, TO* k_cache,
                          TO* v_cache, long long ld, int wq, int wk, int wv, int G, int dk, int dv, int bs, float eps,
                          int write_kv, int n_slots, int* err, const float2* cs_table, int rot, int pairs) {
     __shared__ float red[33];
+    extern __shared__ float staged_row[];
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x, tid = threadIdx.x;
@@ -116,10 +147,12 @@ qkv_rownorm_store_kernel(const TI* qkv, const float* __restrict__ bias, const fl
     float sq = 0.f, sk = 0.f;
     for (int c = tid; c < wq; c += blockDim.x) {
         const float v = to_f<TI>(row[c]) + (bias ? bias[c] : 0.f);
+        if (STAGED) staged_row[c] = v;
         sq += v * v;
     }
     for (int c = tid; c < wk; c += blockDim.x) {
         const float v = to_f<TI>(row[wq + c]) + (bias ? bias[wq + c] : 0.f);
+        if (STAGED) staged_row[wq + c] = v;
         sk += v * v;
     }
     sq = block_sum(sq, red);
@@ -131,7 +164,7 @@ qkv_rownorm_store_kernel(const TI* qkv, const float* __restrict__ bias, const fl
     const int half = rot >> 1;
     const float2* cs = rot ? cs_table + (size_t)t * half : nullptr;
     auto normed = [&](int base, int c, const float* w, float r) {
-        float v = to_f<TI>(row[base + c]) + (bias ? bias[base + c] : 0.f);
+        float v = STAGED ? staged_row[base + c] : to_f<TI>(row[base + c]) + (bias ? bias[base + c] : 0.f);
         if (w) v = v * r * w[c];
         return v;
     };
@@ -176,8 +209,13 @@ RLLM_API int rllm_qkv_rownorm_store(const void* qkv, int in_dt, long long ld, co
     const int ns = (int)(n_slots > 0x7fffffffLL ? 0x7fffffffLL : n_slots);
     // a block per token: few tokens (a decode step) get more threads each, since the row's sums keep it in one block
     const int threads = n < 128 ? 1024 : 256;
+    const size_t smem = (size_t)(H + G) * dk * sizeof(float);
 #define LAUNCH(TI, TO)                                                                                         \
-    return rllm_launch(qkv_rownorm_store_kernel<TI, TO>, dim3(n), dim3(threads), 0, stream, (const TI*)qkv, bias,  \
+    if (smem <= 40 * 1024)                                                                                     \
+        return rllm_launch(qkv_rownorm_store_kernel<TI, TO, true>, dim3(n), dim3(threads), smem, stream, (const TI*)qkv, \
+                           bias, q_norm_w, k_norm_w, slots, (TO*)q_out, (TO*)k_cache, (TO*)v_cache, ld, H * dk, G * dk, \
+                           G * dv, G, dk, dv, bs, eps, write_kv, ns, err, (const float2*)cs_table, rot, pairs);    \
+    return rllm_launch(qkv_rownorm_store_kernel<TI, TO, false>, dim3(n), dim3(threads), 0, stream, (const TI*)qkv, bias, \
                        q_norm_w, k_norm_w, slots, (TO*)q_out, (TO*)k_cache, (TO*)v_cache, ld, H * dk, G * dk, G * dv, \
                        G, dk, dv, bs, eps, write_kv, ns, err, (const float2*)cs_table, rot, pairs)
     if (in_dt == RLLM_F32 && out_dt == RLLM_F32) { LAUNCH(float, float); }
