@@ -991,7 +991,7 @@ RLLM_API long long rllm_retention_state_floats(int H, int dk, int dv) {
 #define MLSTM_SCALARS 4
 
 template <typename TA, int DKMAX, int PASS, int MAXT>
-__global__ void __launch_bounds__(MAXT)
+__global__ void __launch_bounds__(MAXT, (MAXT <= 576 && DKMAX <= 128) ? 2 : 1)
 mlstm_kernel(const float* qp, const float* kp, const float* vp, const float* gp, const float* ip, const float* fp,
              long long ld, const float* __restrict__ i_bias, const float* __restrict__ f_bias, float cap, float q_scale,
              const float* __restrict__ norm_w, float eps, float* state, long long slot_stride,
@@ -1251,18 +1251,20 @@ RLLM_API int rllm_mlstm(const float* qp, const float* kp, const float* vp, const
     return launch_mlstm<TA, DKMAX, MAXT>(n_requests, threads, smem, stream, qp, kp, vp, gp, ip, fp, ld, i_bias, f_bias, \
                                          cap, q_scale, norm_w, eps, state, slot_stride, cu_q, slots, out, H, dk, dv, \
                                          gate_kind, seg)
+    // blocks of up to 576 threads (value heads up to 142 entries and the normaliser's column) are compiled for
+    // two blocks an SM: 128 value columns take 544 threads, one warp more than 512
 #define BY_D(TA)                                                                                               \
     do {                                                                                                       \
-        if (threads > 512) {                                                                                   \
+        if (threads > 576) {                                                                                   \
             if (dkmax == 32) { LAUNCH(TA, 32, 1024); }                                                         \
             if (dkmax == 64) { LAUNCH(TA, 64, 1024); }                                                         \
             if (dkmax == 128) { LAUNCH(TA, 128, 1024); }                                                       \
             LAUNCH(TA, 256, 1024);                                                                             \
         }                                                                                                      \
-        if (dkmax == 32) { LAUNCH(TA, 32, 512); }                                                              \
-        if (dkmax == 64) { LAUNCH(TA, 64, 512); }                                                              \
-        if (dkmax == 128) { LAUNCH(TA, 128, 512); }                                                            \
-        LAUNCH(TA, 256, 512);                                                                                  \
+        if (dkmax == 32) { LAUNCH(TA, 32, 576); }                                                              \
+        if (dkmax == 64) { LAUNCH(TA, 64, 576); }                                                              \
+        if (dkmax == 128) { LAUNCH(TA, 128, 576); }                                                            \
+        LAUNCH(TA, 256, 576);                                                                                  \
     } while (0)
     if (act_dt == RLLM_F32) BY_D(float);
     BY_D(bf16);
