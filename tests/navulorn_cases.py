@@ -236,6 +236,22 @@ def marked_attention(cfg, w, asker, target, boost=12.0):
     return w
 
 
+def marked_memory(cfg, w, marker, gate=16.0, boost=12.0):
+    """Layer 0 (a matrix-memory layer): the input gate opens for the token `marker` alone (its row points along
+    the marker's scaled embedding row, its bias is negative) and the forget gate stays open (no row, a large bias), so
+    what the marker wrote stays the larger part of the memory for hundreds of tokens: a state that is lost,
+    reset or carried wrongly between steps and segments changes every later row."""
+    w = dict(w)
+    H = cfg["layers"][0]["mixer"]["heads"]
+    xa = w["embed"].double()[marker] * cfg["embedding"]["scale"]
+    w["l0.mix.i"] = (torch.outer(torch.ones(H, dtype=torch.float64), xa) * gate / (xa @ xa)).to(w["l0.mix.i"].dtype)
+    w["l0.mix.i.b"] = torch.full((H,), -6.0).to(w["l0.mix.i.b"].dtype)
+    w["l0.mix.o"] = (w["l0.mix.o"].double() * boost).to(w["l0.mix.o"].dtype)     # not drowned by the stream
+    w["l0.mix.f"] = torch.zeros_like(w["l0.mix.f"])
+    w["l0.mix.f.b"] = torch.full((H,), 8.0).to(w["l0.mix.f.b"].dtype)
+    return w
+
+
 def build_engine(cfg, weights, dtype, max_tokens, block_size=8, max_requests=4, use_graphs=None, device="cuda:0"):
     """`use_graphs` None: replay from graphs in float32 only (a replayed step does not show which experts
     it chose, and in bfloat16 the comparison wants to know: see `oracle`)."""

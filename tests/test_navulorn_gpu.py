@@ -626,6 +626,31 @@ def test_sharp_attention_over_every_window(name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["memory", "memory_128"])
+def test_a_token_hundreds_of_places_back_decides_rows_through_the_memory(name, dtype):
+    """The marked memory layer: one token near the start writes most of what the memory holds 600 tokens
+    later.  The prompt whole (cut along time), in portions, and its last 60 tokens decoded: every row against the
+    plain implementation, whose rows far behind the marker change by much more than the tolerance when the
+    marker is another token."""
+    cfg = dict(CASES[name], embedding=dict(CASES[name]["embedding"], scale=8.0))
+    marker = 7
+    w = nc.marked_memory(cfg, nc.make_weights(cfg, 13, stored(dtype)), marker)
+    toks = nc.tokens_for(cfg, 650, 80, avoid=(marker,))
+    without = list(toks)
+    toks[5] = marker
+    ref, other = nc.oracle(cfg, w, toks), nc.oracle(cfg, w, without)
+    moved = [row_error(other[p], ref[p]) for p in range(300, 650)]
+    assert min(moved) > 2 * TOL[dtype] and sorted(moved)[len(moved) // 2] > 5 * TOL[dtype], min(moved)
+    want = list(range(0, 650, 41)) + list(range(600, 650))
+    eng = nc.build_engine(cfg, w, dtype, max_tokens=1024, block_size=16)
+    refs = {"a": ref}
+    compare(run(eng, [([("a", toks, want)], ["a"])]), refs, dtype, "whole")
+    steps = [([("a", t, [len(t) - 1])], []) for t, _ in cut(toks, [290, 2, 130, 7, 200, 21])]
+    compare(run(eng, closing(steps, "a")), refs, dtype, "portions")
+    compare(run(eng, closing([([("a", toks[:590], [589])], [])] + one_by_one("a", toks, 590), "a")), refs, dtype, "decoded")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_the_first_tokens(dtype):
     """Requests of 1, 2 and 3 tokens alone and together: the first token takes the pair table's last row, sees
     itself only, and meets an empty memory whose maximum starts at 0."""
