@@ -852,7 +852,10 @@ def retention(rows, q_off, k_off, v_off, g_off, cs_table, rot, pairs, key_scale,
 def mlstm_state_floats(H: int, dk: int, dv: int) -> int:
     """Floats of a request's matrix-memory state: per head the dk x (dv + 1) memory (the last column is the
     normaliser) padded to the kernel's tile and in its threads' order, then four floats of which the first
-    is the running maximum (recurrent.cu).  No device needed."""
+    is the running maximum (recurrent.cu).  Heads beyond the fast kernel's sizes (keys over 256 entries, values
+    over 254) keep dk x (dv + 1) floats as they are.  No device needed."""
+    if dk > 256 or dv > 254:
+        return H * (dk * (dv + 1) + 4)
     dkmax = 32 if dk <= 32 else 64 if dk <= 64 else 128 if dk <= 128 else 256
     threads = ((dv + 2) // 2 * 8 + 31) // 32 * 32
     return H * (dkmax * (threads // 8 * 2) + 4)
@@ -876,12 +879,12 @@ def mlstm(rows, q_off, k_off, v_off, g_off, i_off, f_off, i_bias, f_bias, cap, q
     for b in (i_bias, f_bias):
         assert b is None or (b.dtype == torch.float32 and b.numel() == H and b.is_contiguous())
     assert norm_w is None or (norm_w.dtype == torch.float32 and norm_w.numel() == H * dv and norm_w.is_contiguous())
-    if dk > 256 or dv > 254:
-        raise KernelError(f"head sizes {dk} x {dv} exceed the matrix-memory kernel's limits of 256 and 254")
+    if 2 * dk + dv + 1 > 12288:
+        raise KernelError(f"head sizes {dk} x {dv} exceed the matrix-memory kernels' shared memory")
     st = _state2d(state)
     per_head = mlstm_state_floats(1, dk, dv)
     assert H * per_head <= st.shape[1]
-    sg = segments
+    sg = segments if (dk <= 256 and dv <= 254) else None          # the kernel for larger heads is not cut along time
     carry = torch.empty((sg.n_items, H, per_head), dtype=torch.float32, device=out.device) if sg is not None else None
     base = rows.data_ptr()
     col = lambda off: c_void_p(base + 4 * off)

@@ -17,7 +17,8 @@
 //           threads + thread; then the previous token's input [width].  Nothing else reads S.
 //   retention:  S of every head, DKMAX * dvp floats a head, in the retention kernel's thread order.
 //   mlstm:  per head DKMAX * dvp floats in the same order, whose value column dv is the normaliser n, then
-//           four floats of which the first is the running maximum m.
+//           four floats of which the first is the running maximum m.  Heads beyond the kernel's sizes: S
+//           [dk][dv + 1] row-major and the four floats.
 #include "common.cuh"
 #include <math.h>
 
@@ -1230,6 +1231,86 @@ static int launch_mlstm(int n_requests, int threads, size_t smem, cudaStream_t s
 #undef ML_ARGS
 }
 
+// ------------------------------------------------------------------ the same recurrence for heads of any size
+// Heads too large for the kernel above (keys over 256 entries, values over 254): one block per (head,
+// request) walks the request's tokens in order with the memory in the slot itself (global memory, L2 for a
+// step's worth): S [dk][dv + 1] row-major, whose column dv is the normaliser, then four floats of which the
+// first is m.  A thread owns every 256th column: S[e][j] = a S[e][j] + k[e] (b v[j]), o[j] += q[e] S[e][j].
+// Slow (the state crosses L2 once a token) and exact in the same order of operations; not cut along time.
+template <typename TA>
+__global__ void __launch_bounds__(256)
+mlstm_generic_kernel(const float* qp, const float* kp, const float* vp, const float* gp, const float* ip, const float* fp,
+                     long long ld, const float* __restrict__ i_bias, const float* __restrict__ f_bias, float cap,
+                     float q_scale, const float* __restrict__ norm_w, float eps, float* state, long long slot_stride,
+                     const int* __restrict__ cu_q, const int* __restrict__ slots, TA* out, int H, int dk, int dv, int gate) {
+    extern __shared__ float sm_g[];
+    __shared__ float red[33];
+    __shared__ float s_gate[3];                           // a, b, exp(-m')
+    const int dvp = dv + 1;
+    float* s_q = sm_g;                                    // [dk]
+    float* s_k = s_q + dk;                                // [dk]
+    float* s_o = s_k + dk;                                // [dvp]
+    const int tid = threadIdx.x, head = blockIdx.x, r = blockIdx.y;
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t per_S = (size_t)dk * dvp;
+    float* S = state + (size_t)slots[r] * slot_stride + (size_t)head * (per_S + MLSTM_SCALARS);
+    float m_run = S[per_S];
+    const size_t qcol = (size_t)head * dk, vcol = (size_t)head * dv;
+    const float ib = i_bias ? i_bias[head] : 0.f, fb = f_bias ? f_bias[head] : 0.f;
+    for (int t = cu_q[r]; t < cu_q[r + 1]; ++t) {
+        for (int e = tid; e < dk; e += blockDim.x) {
+            s_q[e] = qp[(size_t)t * ld + qcol + e];
+            s_k[e] = kp[(size_t)t * ld + qcol + e];
+        }
+        if (tid == 0) {
+            const float xi = ip[(size_t)t * ld + head] + ib, xf = fp[(size_t)t * ld + head] + fb;
+            const float ig = cap > 0.f ? cap * tanhf(xi / cap) : xi;
+            const float fg = -softplus_f(-(cap > 0.f ? cap * tanhf(xf / cap) : xf));
+            const float mn = fmaxf(fg + m_run, ig);
+            s_gate[0] = expf(fg + m_run - mn);
+            s_gate[1] = expf(ig - mn);
+            s_gate[2] = expf(-mn);
+            m_run = mn;
+        }
+        __syncthreads();
+        const float a = s_gate[0], b = s_gate[1];
+        for (int j = tid; j < dvp; j += blockDim.x) {
+            const float vj = (j < dv ? vp[(size_t)t * ld + vcol + j] : 1.f) * b;
+            float acc = 0.f;
+            for (int e = 0; e < dk; ++e) {
+                const float sv = a * S[(size_t)e * dvp + j] + s_k[e] * vj;
+                S[(size_t)e * dvp + j] = sv;
+                acc += s_q[e] * sv;
+            }
+            s_o[j] = acc;
+        }
+        __syncthreads();
+        const float nq = s_o[dv] * q_scale;
+        const float inv = q_scale / (fmaxf(fabsf(nq), s_gate[2]) + 1e-6f);
+        float ss = 0.f;
+        for (int j = tid; j < dv; j += blockDim.x) {
+            const float o = s_o[j] * inv;
+            ss += o * o;
+        }
+        ss = block_sum(ss, red);
+        const float rs = 1.0f / sqrtf(ss / (float)dv + eps);
+        for (int j = tid; j < dv; j += blockDim.x) {
+            float v = s_o[j] * inv * rs;
+            if (norm_w) v *= norm_w[vcol + j];
+            if (gate) {
+                const float gz = gp[(size_t)t * ld + vcol + j];
+                v *= gate == 1 ? silu_f(gz) : 1.0f / (1.0f + expf(-gz));
+            }
+            out[(size_t)t * H * dv + vcol + j] = from_f<TA>(v);
+        }
+        __syncthreads();                                  // s_q, s_k, s_o and the gates are free again
+    }
+    if (tid == 0) S[per_S] = m_run;
+}
+
+static inline bool mlstm_fits_fast(int dk, int dv) { return dk <= 256 && dv <= 254; }
+
 // q, k [n, H*dk], v, gate [n, H*dv], the gates' pre-activations ip, fp [n, H]: float32 columns of one
 // projection (rows ld apart); i_bias, f_bias [H] or null; norm_w [H*dv] or null; gate_kind 0: none, 1: silu,
 // 2: sigmoid.  carry needs n_items * H * (DKMAX * dvp + 4) floats.
@@ -1240,8 +1321,18 @@ RLLM_API int rllm_mlstm(const float* qp, const float* kp, const float* vp, const
                         const int* seg_t0, const int* seg_t1, const int* seg_req, const int* seg_flags,
                         const int* req_item0, const int* req_items, int n_items, float* carry, cudaStream_t stream) {
     if (n_requests <= 0) return 0;
-    if (dk <= 0 || dk > 256 || dv <= 0 || dv > 254 || H <= 0 || cap < 0.f || (gate_kind && !gp) || !ip || !fp)
-        return (int)cudaErrorInvalidValue;
+    if (dk <= 0 || dv <= 0 || H <= 0 || cap < 0.f || (gate_kind && !gp) || !ip || !fp) return (int)cudaErrorInvalidValue;
+    if (!mlstm_fits_fast(dk, dv)) {
+        const size_t smem_g = ((size_t)2 * dk + dv + 1) * sizeof(float);
+        if (smem_g > 48 * 1024) return (int)cudaErrorInvalidValue;
+        if (act_dt == RLLM_F32)
+            return rllm_launch(mlstm_generic_kernel<float>, dim3(H, n_requests), dim3(256), smem_g, stream, qp, kp, vp, gp, ip,
+                               fp, ld, i_bias, f_bias, cap, q_scale, norm_w, eps, state, slot_stride, cu_q, slots,
+                               (float*)out, H, dk, dv, gate_kind);
+        return rllm_launch(mlstm_generic_kernel<bf16>, dim3(H, n_requests), dim3(256), smem_g, stream, qp, kp, vp, gp, ip, fp,
+                           ld, i_bias, f_bias, cap, q_scale, norm_w, eps, state, slot_stride, cu_q, slots, (bf16*)out, H, dk,
+                           dv, gate_kind);
+    }
     const int dkmax = ret_dkmax(dk), threads = mlstm_threads(dv), dvp = threads / RET_PARTS * 2;
     TimeSegments seg = {seg_t0, seg_t1, seg_req, seg_flags, req_item0, req_items, carry, nullptr, n_items};
     if (n_items > 0 && (!seg_t0 || !seg_t1 || !seg_req || !seg_flags || !req_item0 || !req_items || !carry))
@@ -1274,6 +1365,7 @@ RLLM_API int rllm_mlstm(const float* qp, const float* kp, const float* vp, const
 
 // Floats of a request's mLSTM state for H heads of dk x dv (no device needed).
 RLLM_API long long rllm_mlstm_state_floats(int H, int dk, int dv) {
+    if (!mlstm_fits_fast(dk, dv)) return (long long)H * ((long long)dk * (dv + 1) + MLSTM_SCALARS);
     return (long long)H * ((long long)ret_dkmax(dk) * (mlstm_threads(dv) / RET_PARTS * 2) + MLSTM_SCALARS);
 }
 

@@ -13,7 +13,8 @@ For input rows h [n, d] of one request in order, H heads with keys of dk and val
     out = ((o / rms(o) per head, eps inside the root) * norm_w * gate(h Wg^T)) Wo^T
 
 State per request (float32): S and n of every head in the kernel's own order, and m, kept from step to
-step (csrc/recurrent.cu).  Parameters: hidden_size, num_heads, head_dim, v_head_dim, gate_cap (0: the
+step (csrc/recurrent.cu).  Key heads up to 256 and value heads up to 254 entries take the fast kernel (cut
+along time for long portions); larger heads a plain kernel that walks the tokens with the memory in the slot.  Parameters: hidden_size, num_heads, head_dim, v_head_dim, gate_cap (0: the
 gates are not capped), q_scale, eps, gate ("sigmoid", "silu" or None).  Tensors under <prefix>: q, k
 [H*dk, d]; v, g [H*dv, d]; i, f [H, d]; i.b, f.b [H]; norm [H*dv]; o [d, H*dv].  q, k, v, the gate and the
 two gate rows are one stacked product (rows of zeros up to a multiple of 8) whose result stays float32;
@@ -44,8 +45,8 @@ class MatrixMemory(Mixer):
         self.gate = p.get("gate", "sigmoid")
         if self.gate not in ops.GATES:
             raise PartError(f"mlstm: gate {self.gate!r} is not known")
-        if self.dk > 256 or self.dv > 254:
-            raise PartError("mlstm: key heads up to 256 entries, value heads up to 254")
+        if 2 * self.dk + self.dv + 1 > 12288:
+            raise PartError("mlstm: head sizes beyond the kernels' shared memory (2 dim + vdim up to 12,287)")
         if self.cap < 0:
             raise PartError("mlstm: gate_cap must not be negative")
         self.has_gate = bool(ops.GATES[self.gate])

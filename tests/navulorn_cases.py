@@ -75,6 +75,7 @@ CASES = {
     "memory_48": config([mem(2, 48, 40, cap=15.0)], width=40, vocab=67, eps=3e-6),
     "memory_wide_values": config([mem(1, 16, 136, cap=4.0, mlp=moe(12, 3, 3))], width=32, vocab=47),
     "memory_128": config([mem(2, 128, 64)], width=48, vocab=71),
+    "memory_one_wide_head": config([mem(1, 24, 272, cap=11.0, mlp=dense(28))], width=36, vocab=51, alpha=1.5),   # beyond the fast kernel
     "moe": config([mem(2, 8, 8, mlp=moe(12, 12, 4))], width=20, vocab=47, alpha=1.5),
     "moe_one_each": config([att(2, 1, 12, 12, 6, 6, mlp=moe(10, 5, 1))], width=22, vocab=43),
     # head sizes 64 and 128 with values of the same size (the tensor-core attention kernels in bfloat16) and

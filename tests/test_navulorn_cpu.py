@@ -118,13 +118,15 @@ def test_state_sizes():
     assert ops.mlstm_state_floats(2, 48, 40) == 2 * (64 * 48 + 4)
     assert ops.mlstm_state_floats(1, 128, 64) == 128 * 72 + 4
     assert ops.mlstm_state_floats(3, 16, 254) == 3 * (32 * 256 + 4)
+    assert ops.mlstm_state_floats(2, 16, 255) == 2 * (16 * 256 + 4)          # beyond the fast kernel: as it is
+    assert ops.mlstm_state_floats(1, 257, 8) == 257 * 9 + 4
     from rllm_b200.csrc import build
     try:
         lib = build.load("recur")
     except Exception:
         pytest.skip("the recurrent kernels' library cannot be built here")
     lib.rllm_mlstm_state_floats.restype = __import__("ctypes").c_longlong
-    for H, dk, dv in ((1, 8, 12), (2, 48, 40), (4, 128, 64), (1, 200, 254), (3, 33, 1)):
+    for H, dk, dv in ((1, 8, 12), (2, 48, 40), (4, 128, 64), (1, 200, 254), (3, 33, 1), (2, 16, 255), (1, 300, 300)):
         assert lib.rllm_mlstm_state_floats(H, dk, dv) == ops.mlstm_state_floats(H, dk, dv)
 
 

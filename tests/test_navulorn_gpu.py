@@ -348,7 +348,7 @@ def _memory_weights(H, dk, dv, d, g):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,dk,dv,cap", [(3, 8, 12, 8.0), (2, 48, 40, 15.0), (1, 16, 136, 3.0), (2, 128, 64, 6.0), (1, 200, 254, 9.0),
-                                         (4, 33, 1, 2.0)])
+                                         (4, 33, 1, 2.0), (1, 16, 300, 5.0), (2, 260, 20, 7.0)])      # the last two: the plain kernel
 def test_matrix_memory_kernel(dtype, H, dk, dv, cap):
     """Three requests of 37, 1 and 5 tokens in one launch, each in two calls (the state is carried in its
     slot), against the token-by-token recurrence; then a slot that was used is zeroed and used again."""
