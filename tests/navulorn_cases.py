@@ -84,6 +84,9 @@ CASES = {
                       vocab=113),
     "heads128": config([att(2, 1, 128, 128, 64, 50, base=50000.0), mem(2, 64, 128)], width=48, vocab=103, alpha=4.0),
     "latent64": config([lat(4, 16, 16, 24, 64, 45, mlp=dense(40)), lat(2, 8, 32, 8, 128, 19)], width=64, vocab=97),
+    # sizes that are no multiple of 2, 4 or 8 wherever the design allows it
+    "odd_sizes": config([att(3, 1, 10, 7, 6, 4, mlp=moe(9, 3, 2)), lat(3, 5, 2, 3, 7, 5, mlp=dense(11)), mem(3, 5, 3, cap=5.0),
+                         att(1, 1, 6, 9, 2, 3)], width=37, vocab=45, alpha=1.7, bigram=(13, 3, 2), softcap=9.0),
     # everything together, in two orders
     "stack": config([mem(4, 16, 24, mlp=dense(96)),
                      att(6, 2, 32, 16, 16, 13, scaling=LLAMA, base=300.0, mlp=moe(24, 8, 3)),
