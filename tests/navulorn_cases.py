@@ -82,6 +82,8 @@ CASES = {
     # latents of 64 and 128 entries with key rows that are multiples of 16 (the tensor-core latent kernel)
     "heads64": config([att(8, 2, 64, 64, 48, 21, mlp=dense(72)), att(2, 2, 64, 64, 64, 40, scaling=LLAMA)], width=64,
                       vocab=113),
+    "heads_tiny_windows": config([att(4, 2, 64, 64, 32, 3, mlp=dense(24)), att(2, 1, 128, 128, 128, 1), att(4, 4, 64, 64, 2, 130)],
+                                 width=48, vocab=83, alpha=2.5, bigram=(29, 4, 9)),
     "heads128": config([att(2, 1, 128, 128, 64, 50, base=50000.0), mem(2, 64, 128)], width=48, vocab=103, alpha=4.0),
     "latent64": config([lat(4, 16, 16, 24, 64, 45, mlp=dense(40)), lat(2, 8, 32, 8, 128, 19)], width=64, vocab=97),
     # sizes that are no multiple of 2, 4 or 8 wherever the design allows it
