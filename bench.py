@@ -192,7 +192,7 @@ def navulorn_shape(width: int) -> dict:
     layers = [{"type": "mlstm", "mixer": mem, "mlp": dense}, {"type": "attention", "mixer": att, "mlp": moe},
               {"type": "latent_attention", "mixer": lat, "mlp": moe}, {"type": "attention", "mixer": att, "mlp": dense}] * 2
     return {"architecture": "Navulorn", "vocab": 32768, "width": width, "layers": layers, "norm": {"eps": 1e-6},
-            "embedding": {"scale": 8.0, "bigram": {"buckets": 32749, "mul_prev": 31, "mul_cur": 7}}, "postln_alpha": 2.0,
+            "embedding": {"scale": 8.0, "bigram": {"buckets": 32749, "mul_prev": 53, "mul_cur": 11}}, "postln_alpha": 2.0,
             "logit_softcap": 30.0}
 
 

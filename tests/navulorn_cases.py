@@ -80,7 +80,7 @@ CASES = {
     "moe_one_each": config([att(2, 1, 12, 12, 6, 6, mlp=moe(10, 5, 1))], width=22, vocab=43),
     # head sizes 64 and 128 with values of the same size (the tensor-core attention kernels in bfloat16) and
     # latents of 64 and 128 entries with key rows that are multiples of 16 (the tensor-core latent kernel)
-    "heads64": config([att(8, 2, 64, 64, 48, 21, mlp=dense(72)), att(2, 2, 64, 64, 64, 40, scaling=LLAMA)], width=64,
+    "heads64": config([att(8, 2, 64, 64, 48, 21, mlp=dense(72)), att(2, 2, 64, 64, 64, 44, scaling=LLAMA)], width=64,
                       vocab=113),
     "heads_tiny_windows": config([att(4, 2, 64, 64, 32, 3, mlp=dense(24)), att(2, 1, 128, 128, 128, 1), att(4, 4, 64, 64, 2, 130)],
                                  width=48, vocab=83, alpha=2.5, bigram=(29, 4, 9)),
@@ -97,7 +97,7 @@ CASES = {
                      mem(2, 24, 40, cap=10.0, mlp=moe(16, 6, 2)),
                      lat(2, 8, 8, 8, 16, 11)], width=64, vocab=131, alpha=2.5, scale=4.0),
     "stack_attention_first": config([att(4, 4, 8, 10, 2, 10, mlp=moe(20, 4, 2)), lat(3, 10, 6, 6, 12, 25, mlp=dense(36)),
-                                     mem(3, 12, 18, cap=6.0), att(3, 1, 20, 10, 10, 40, mlp=dense(36))], width=40,
+                                     mem(3, 12, 18, cap=6.0), att(3, 1, 20, 10, 10, 44, mlp=dense(36))], width=40,
                                     vocab=89, alpha=2.0, bigram=(53, 2, 9)),
 }
 

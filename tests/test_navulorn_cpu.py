@@ -108,7 +108,7 @@ def test_what_the_layers_ask_of_the_cache():
     _, bare, _ = _needs("attention_no_window")
     assert len(bare) == 1 and bare[0] == PagedKVNeed(2, 12, 0, 0, 4)
     _, same, _ = _needs("heads64")
-    assert same[0] == PagedKVNeed(2, 64, 21, 0, 0) and same[1] == PagedKVNeed(2, 64, 40, 0, 0)
+    assert same[0] == PagedKVNeed(2, 64, 21, 0, 0) and same[1] == PagedKVNeed(2, 64, 44, 0, 0)
 
 
 def test_state_sizes():

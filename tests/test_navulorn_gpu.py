@@ -707,7 +707,7 @@ def test_long_decoding_through_graph_replay(dtype):
 REAL = nc.config([nc.mem(8, 64, 128, mlp=nc.dense(1536)),
                   nc.att(8, 2, 128, 128, 64, 100, scaling=(8.0, 1.0, 4.0, 256), mlp=nc.moe(256, 32, 4)),
                   nc.lat(8, 64, 32, 64, 256, 70, mlp=nc.dense(1024)),
-                  nc.att(16, 4, 64, 64, 64, 33, mlp=nc.moe(384, 8, 2))], width=1024, vocab=1531, scale=6.0, bigram=(997, 31, 7))
+                  nc.att(16, 4, 64, 64, 64, 33, mlp=nc.moe(384, 8, 2))], width=1024, vocab=1531, scale=6.0, bigram=(997, 29, 5))
 
 
 @pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
