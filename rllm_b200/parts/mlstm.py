@@ -6,7 +6,7 @@ For input rows h [n, d] of one request in order, H heads with keys of dk and val
     q = h Wq^T * q_scale,  k = h Wk^T  ([H, dk]),  v = h Wv^T  ([H, dv])
     per head, from two more rows of the projection and their biases:
         i = cap * tanh((h . w_i + b_i) / cap),   f = logsigmoid(cap * tanh((h . w_f + b_f) / cap))
-    per head, S [dk, dv], n [dk] and m starting at zero (m at 0, not at minus infinity):
+    per head, S [dk, dv], n [dk] and the running maximum m, all three zero before the first token:
         m_t = max(f + m_(t-1), i)
         S_t = exp(f + m_(t-1) - m_t) S_(t-1) + exp(i - m_t) k v^T       n_t likewise with k alone
         o = S_t^T q / (max(|n_t . q|, exp(-m_t)) + 1e-6)
